@@ -1,0 +1,433 @@
+// Paged causal GQA attention for the bfloat16 path, compiled per head size
+// (-DTGE_HEAD_DIM=...).  One kernel serves prompt portions and decode rows.
+//
+// A block owns one tile of query rows of one kv head of one portion: the rows
+// are (query, head-of-group) pairs, query-major, so every K/V tile fetched
+// from the pages is used by all the query heads that share it (the structure
+// of the reference's group kernel, src/cpu/scalar/attention_scalar.cpp:117-199).
+// K/V stream through shared memory in tiles of 64 positions (page-aligned; one
+// page-table lookup per 16-byte chunk copy, hoisted out of the inner product),
+// scores and the running maximum/sum are float32 (online softmax, the same
+// update the reference uses when it merges chunk states,
+// src/models/qwen2.cpp:1469-1522), P is rounded to bfloat16 only as the
+// operand of the P.V product.  With more than one split along the keys a block
+// writes its unnormalised state (m, l, acc) and a second kernel merges the
+// splits in split order.
+//
+// Masking is by absolute position: key t is visible to the query at position p
+// when t <= p and, with a window w > 0, t > p - w.
+#include "common.cuh"
+
+#ifndef TGE_HEAD_DIM
+#error "compile with -DTGE_HEAD_DIM=<multiple of 16>"
+#endif
+
+namespace {
+
+constexpr int HD = TGE_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int BKV = 64;              // key positions per shared-memory tile
+constexpr int ROW_ELEMS = HD + 8;    // padded row: an odd count of 16-byte chunks keeps ldmatrix conflict-free
+constexpr int CHUNKS = HD / 8;       // 16-byte chunks per row
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k_pages;
+  const __nv_bfloat16* v_pages;
+  const int* block_table;
+  const int* q_start;
+  const int* start_pos;
+  __nv_bfloat16* out;
+  float* partial_o;
+  float* partial_ml;
+  int* status;
+  int q_stride, out_stride;
+  int max_pages, num_pages, page_size;
+  int num_seqs, total_tokens;
+  int heads, kv_heads, group, bq;
+  int window, split_tokens, num_splits;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copies positions [k0, k0 + BKV) of one kv head into a shared tile; positions
+// outside [lo, hi) are zero-filled so that masked columns never meet NaNs.
+template <int NWARPS>
+__device__ __forceinline__ void load_tile(const AttnParams& p, const __nv_bfloat16* pages, const int* table, int kvh,
+                                          __nv_bfloat16* tile, int k0, int lo, int hi, bool& bad_page) {
+  for (int c = threadIdx.x; c < BKV * CHUNKS; c += NWARPS * 32) {
+    const int j = c / CHUNKS, part = c - j * CHUNKS;
+    const int kpos = k0 + j;
+    const uint32_t dst = smem_u32(tile + j * ROW_ELEMS + part * 8);
+    const void* src = pages;
+    int bytes = 0;
+    if (kpos >= lo && kpos < hi) {
+      const int page_index = kpos / p.page_size;
+      const int page = page_index < p.max_pages ? table[page_index] : -1;
+      if (page >= 0 && page < p.num_pages) {
+        src = pages + (((size_t)page * p.kv_heads + kvh) * p.page_size + (kpos - page_index * p.page_size)) * HD + part * 8;
+        bytes = 16;
+      } else {
+        bad_page = true;
+      }
+    }
+    cp_async16(dst, src, bytes);
+  }
+}
+
+template <int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [2][BKV][ROW_ELEMS]
+  __nv_bfloat16* sV = sK + 2 * BKV * ROW_ELEMS;                             // [2][BKV][ROW_ELEMS]
+  __shared__ int tile_info[2];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+
+  // which portion and which tile of its queries this block owns
+  if (tid == 0) {
+    int remaining = blockIdx.x, seq = -1, tile = 0;
+    for (int s = 0; s < p.num_seqs; ++s) {
+      const int q_len = p.q_start[s + 1] - p.q_start[s];
+      const int tiles = (q_len + p.bq - 1) / p.bq;
+      if (remaining < tiles) { seq = s; tile = remaining; break; }
+      remaining -= tiles;
+    }
+    tile_info[0] = seq;
+    tile_info[1] = tile;
+  }
+  __syncthreads();
+  const int seq = tile_info[0];
+  if (seq < 0) return;
+  const int q_first = tile_info[1] * p.bq;                 // first query of the tile, within the portion
+  const int q_begin = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - q_begin;
+  const int q_count = min(p.bq, q_len - q_first);
+  const int pos0 = p.start_pos[seq] + q_first;             // position of the tile's first query
+  const int* table = p.block_table + (size_t)seq * p.max_pages;
+
+  // key range of the block: union over its rows, cut to this split
+  int lo = p.window > 0 ? max(pos0 - p.window + 1, 0) : 0;
+  int hi = pos0 + q_count;                                 // exclusive
+  if (p.num_splits > 1) {
+    lo = max(lo, split * p.split_tokens);
+    hi = min(hi, (split + 1) * p.split_tokens);
+  }
+  if (lo >= hi) return;
+
+  // this thread's two rows
+  int row_token[2], row_pos[2], row_head[2];
+  bool row_valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g8 + 8 * i;
+    const int qi = r / p.group, gg = r - qi * p.group;
+    row_valid[i] = qi < q_count;
+    row_token[i] = q_begin + q_first + (row_valid[i] ? qi : 0);
+    row_pos[i] = pos0 + qi;
+    row_head[i] = kvh * p.group + gg;
+  }
+
+  // Q fragments (A operand), straight from global memory
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const __nv_bfloat16* src = p.q + (size_t)row_token[i] * p.q_stride + (size_t)row_head[i] * HD + kc * 16 + 2 * t4;
+      qf[kc][i] = row_valid[i] ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+      qf[kc][i + 2] = row_valid[i] ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+    }
+  }
+
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[d][e] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+  bool bad_page = false;
+  const int k_first = lo / BKV * BKV;
+  const int num_tiles = (hi - k_first + BKV - 1) / BKV;
+  load_tile<NWARPS>(p, p.k_pages, table, kvh, sK, k_first, lo, hi, bad_page);
+  load_tile<NWARPS>(p, p.v_pages, table, kvh, sV, k_first, lo, hi, bad_page);
+  cp_async_commit();
+
+  for (int it = 0; it < num_tiles; ++it) {
+    const int stage = it & 1;
+    const int k0 = k_first + it * BKV;
+    if (it + 1 < num_tiles) {
+      load_tile<NWARPS>(p, p.k_pages, table, kvh, sK + (stage ^ 1) * BKV * ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
+      load_tile<NWARPS>(p, p.v_pages, table, kvh, sV + (stage ^ 1) * BKV * ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const __nv_bfloat16* tK = sK + stage * BKV * ROW_ELEMS;
+    const __nv_bfloat16* tV = sV + stage * BKV * ROW_ELEMS;
+
+    // S = Q K^T for 16 rows x 64 keys
+    float s_acc[BKV / 8][4];
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_acc[n][e] = 0.0f;
+#pragma unroll
+    for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+      for (int nt = 0; nt < BKV / 8; nt += 2) {
+        const int mi = lane >> 3;
+        const int n = (nt + (mi >> 1)) * 8 + (lane & 7);
+        const int kofs = kc * 16 + (mi & 1) * 8;
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4(smem_u32(tK + n * ROW_ELEMS + kofs), r0, r1, r2, r3);
+        mma_bf16(s_acc[nt], qf[kc], r0, r1);
+        mma_bf16(s_acc[nt + 1], qf[kc], r2, r3);
+      }
+    }
+
+    // mask, running maximum, exponentials (float32, base-2 with the scale folded in)
+    float m_new[2], corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int first_key = p.window > 0 ? row_pos[i] - p.window + 1 : 0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < BKV / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kpos = k0 + n * 8 + 2 * t4 + e;
+          const bool visible = row_valid[i] && kpos <= row_pos[i] && kpos >= first_key && kpos >= lo && kpos < hi;
+          const float s = visible ? s_acc[n][2 * i + e] * p.scale_log2 : -INFINITY;
+          s_acc[n][2 * i + e] = s;
+          mx = fmaxf(mx, s);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      m_new[i] = fmaxf(m_run[i], mx);
+      const float m_use = m_new[i] == -INFINITY ? 0.0f : m_new[i];
+      corr[i] = exp2f(m_run[i] - m_use);
+      float sum = 0.0f;
+#pragma unroll
+      for (int n = 0; n < BKV / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float pv = exp2f(s_acc[n][2 * i + e] - m_use);
+          s_acc[n][2 * i + e] = pv;
+          sum += pv;
+        }
+      }
+      l_run[i] = l_run[i] * corr[i] + sum;
+      m_run[i] = m_new[i];
+    }
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
+      o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
+    }
+
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < BKV / 16; ++kk) {
+      uint32_t pf[4];
+      pf[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+      pf[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+      pf[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+      pf[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; dt += 2) {
+        const int mi = lane >> 3;
+        const int key = kk * 16 + (mi & 1) * 8 + (lane & 7);
+        const int d = (dt + (mi >> 1)) * 8;
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4_trans(smem_u32(tV + key * ROW_ELEMS + d), r0, r1, r2, r3);
+        mma_bf16(o_acc[dt], pf, r0, r1);
+        mma_bf16(o_acc[dt + 1], pf, r2, r3);
+      }
+    }
+    __syncthreads();
+  }
+  if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
+
+  // finish: total the sums over the four lanes that share a row
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!row_valid[i]) continue;
+    if (p.num_splits == 1) {
+      const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+      __nv_bfloat16* dst = p.out + (size_t)row_token[i] * p.out_stride + (size_t)row_head[i] * HD;
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d) {
+        *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * t4) =
+            pack_bf16(o_acc[d][2 * i] * inv, o_acc[d][2 * i + 1] * inv);
+      }
+    } else {
+      const size_t slot = ((size_t)split * p.total_tokens + row_token[i]) * p.heads + row_head[i];
+      float* dst = p.partial_o + slot * HD;
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d) {
+        *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o_acc[d][2 * i], o_acc[d][2 * i + 1]);
+      }
+      if (t4 == 0) {
+        p.partial_ml[slot * 2] = m_run[i];
+        p.partial_ml[slot * 2 + 1] = l_run[i];
+      }
+    }
+  }
+}
+
+// Merges the split states of one (token, head): out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s,
+// over the splits that hold keys visible to the row, in split order.
+__global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
+                                       const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
+                                       int out_stride, int total_tokens, int heads, int window, int split_tokens,
+                                       int num_splits) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int pos = positions[t];
+  const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
+  const int s_lo = first_key / split_tokens;
+  const int s_hi = min(pos / split_tokens, num_splits - 1);
+  float m = -INFINITY;
+  for (int s = s_lo; s <= s_hi; ++s) {
+    const size_t slot = ((size_t)s * total_tokens + t) * heads + h;
+    m = fmaxf(m, partial_ml[slot * 2]);
+  }
+  const float m_use = m == -INFINITY ? 0.0f : m;
+  float l = 0.0f;
+  for (int s = s_lo; s <= s_hi; ++s) {
+    const size_t slot = ((size_t)s * total_tokens + t) * heads + h;
+    l += exp2f(partial_ml[slot * 2] - m_use) * partial_ml[slot * 2 + 1];
+  }
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = s_lo; s <= s_hi; ++s) {
+      const size_t slot = ((size_t)s * total_tokens + t) * heads + h;
+      acc += exp2f(partial_ml[slot * 2] - m_use) * partial_o[slot * HD + d];
+    }
+    out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int NWARPS>
+int launch(const AttnParams& p, int tiles, cudaStream_t stream) {
+  const size_t smem = (size_t)4 * BKV * ROW_ELEMS * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+      tge_set_error("attention_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+      return -2;
+    }
+    configured = true;
+  }
+  dim3 grid(tiles, p.kv_heads, p.num_splits);
+  attention_mma_kernel<NWARPS><<<grid, NWARPS * 32, smem, stream>>>(p);
+  return tge_check_launch("attention_mma");
+}
+
+}  // namespace
+
+TGE_API int tge_attention_mma_head_dim() { return HD; }
+
+// Rows of scratch a call needs: float32 [splits, tokens, heads, HD] for acc and [splits, tokens, heads, 2] for (m, l).
+TGE_API long long tge_attention_mma_scratch_floats(int tokens, int heads, int num_splits) {
+  return num_splits > 1 ? (long long)num_splits * tokens * heads * (HD + 2) : 0;
+}
+
+// q: [tokens, heads*HD] with row stride q_stride (elements); pages: [num_pages, kv_heads, page_size, HD].
+// q_start [num_seqs+1], start_pos [num_seqs], positions [tokens] are int32 on the device.
+// max_q_len / max_ctx_len are host-side bounds used only for launch geometry.
+// split_tokens: 0 = one split; else a multiple of 64 (keys per split).  scratch: see above.
+TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                              const int* block_table, int max_pages, int num_pages, int page_size,
+                              const int* q_start, const int* start_pos, const int* positions, int num_seqs,
+                              int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
+                              int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
+                              cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && num_seqs >= 0, "attention_mma: negative sizes");
+  TGE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+              "attention_mma: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
+  const int group = heads / kv_heads;
+  TGE_REQUIRE(group <= 64, "attention_mma: %d query heads per kv head exceed the 64 rows of a tile", group);
+  TGE_REQUIRE(page_size > 0 && BKV % page_size == 0, "attention_mma: page size %d must divide %d", page_size, BKV);
+  TGE_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0, "attention_mma: odd row strides");
+  TGE_REQUIRE(((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0) && ((uintptr_t)k_pages % 16 == 0) &&
+                  ((uintptr_t)v_pages % 16 == 0), "attention_mma: misaligned tensors");
+  TGE_REQUIRE(window >= 0 && split_tokens >= 0 && split_tokens % BKV == 0,
+              "attention_mma: keys per split %d must be a multiple of %d", split_tokens, BKV);
+  if (tokens == 0 || num_seqs == 0) return 0;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
+  p.block_table = block_table; p.q_start = q_start; p.start_pos = start_pos;
+  p.out = (__nv_bfloat16*)out; p.status = status;
+  p.q_stride = q_stride; p.out_stride = out_stride;
+  p.max_pages = max_pages; p.num_pages = num_pages; p.page_size = page_size;
+  p.num_seqs = num_seqs; p.total_tokens = tokens;
+  p.heads = heads; p.kv_heads = kv_heads; p.group = group;
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  int num_splits = 1;
+  if (split_tokens > 0 && max_ctx_len > split_tokens) num_splits = (max_ctx_len + split_tokens - 1) / split_tokens;
+  p.split_tokens = split_tokens > 0 ? split_tokens : max_ctx_len;
+  p.num_splits = num_splits;
+  TGE_REQUIRE(num_splits == 1 || scratch != nullptr, "attention_mma: %d splits need scratch memory", num_splits);
+  p.partial_o = scratch;
+  p.partial_ml = scratch ? scratch + (size_t)num_splits * tokens * heads * HD : nullptr;
+
+  // rows per block: one warp (16 rows) per block when every portion is a single token and the group fits
+  int nwarps = 4;
+  if (max_q_len <= 1) nwarps = group <= 16 ? 1 : (group <= 32 ? 2 : 4);
+  const int rows = nwarps * 16;
+  p.bq = rows / group;
+  const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;  // upper bound over any cut into portions
+  int rc;
+  if (nwarps == 1) rc = launch<1>(p, tiles, stream);
+  else if (nwarps == 2) rc = launch<2>(p, tiles, stream);
+  else rc = launch<4>(p, tiles, stream);
+  if (rc != 0) return rc;
+  if (num_splits > 1) {
+    dim3 grid(tokens, heads);
+    attention_merge_kernel<<<grid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
+        p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+    return tge_check_launch("attention_merge");
+  }
+  return 0;
+}

@@ -1,0 +1,76 @@
+// Shared helpers for the sm_100a kernels of this engine.
+//
+// Conventions every kernel file follows:
+//  * entry points are extern "C", take raw device pointers plus a cudaStream_t,
+//    validate their arguments on the host and return 0 or a negative code after
+//    storing a message readable through tge_last_error();
+//  * a kernel that can meet a bad index (token id, page id) does not touch
+//    memory with it: it records the fault in a caller-supplied status word and
+//    skips the access, so a bad input never becomes a memory fault;
+//  * statistics (norm sums, softmax, rotation, residual sums) are float32.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TGE_API extern "C" __attribute__((visibility("default")))
+
+// Status word bits set by kernels (one int32 in device memory, owned by the caller).
+enum TgeStatusBits : int {
+  TGE_STATUS_BAD_TOKEN = 1,      // token id outside the vocabulary
+  TGE_STATUS_BAD_PAGE = 2,       // page id outside the pool
+  TGE_STATUS_BAD_ROW = 4,        // row index outside the batch
+  TGE_STATUS_WAIT_TIMEOUT = 8,   // a bounded device-side wait gave up
+};
+
+void tge_set_error(const char* fmt, ...);
+int tge_check_launch(const char* what);
+
+#define TGE_REQUIRE(cond, ...)            \
+  do {                                    \
+    if (!(cond)) {                        \
+      tge_set_error(__VA_ARGS__);         \
+      return -1;                          \
+    }                                     \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// Sum over a block in a fixed order: a butterfly inside each warp, then the
+// warp totals added in warp order by every thread.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.0f;
+  for (int w = 0; w < warps; ++w) total += scratch[w];
+  return total;
+}

@@ -1,0 +1,188 @@
+// Embedding, RMSNorm, residual add, rotary rotation fused with the cache store.
+//
+// Formulas follow the reference's scalar kernels:
+//   rms norm     src/cpu/scalar/norm_rope_scalar.cpp:8-21
+//   rotate-half  src/cpu/scalar/norm_rope_scalar.cpp:23-41
+//   cache write  src/models/qwen2.cpp:2308-2329 (rotated K and plain V, after the bias)
+//   embedding    src/models/qwen2.cpp:1143-1152
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding: x[t, :] = table[ids[t], :] as float32
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_TOKEN);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.0f;
+    return;
+  }
+  const T* src = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float<T>(src[i]);
+}
+
+TGE_API int tge_embedding(const void* table, int is_bf16, const int* ids, float* out, int tokens,
+                          int hidden, int vocab, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes tokens=%d hidden=%d vocab=%d",
+              tokens, hidden, vocab);
+  if (tokens == 0) return 0;
+  if (is_bf16)
+    embedding_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+  else
+    embedding_kernel<float><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
+  return tge_check_launch("embedding");
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm over the float32 stream; output in the run dtype.
+//   s = sum x_i^2 ; scale = 1 / sqrt(s / dim + eps) ; out_i = x_i * scale * w_i
+// One block per output row; optional row gather (rows[r] = source row).
+// ---------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                               const int* __restrict__ rows, TOut* __restrict__ out, int hidden,
+                               int src_rows, float eps, int* status) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  int src = rows ? rows[r] : r;
+  if (src < 0 || src >= src_rows) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+    src = 0;
+  }
+  const float* in = x + (size_t)src * hidden;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = in[i];
+    sum = fmaf(v, v, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = 1.0f / sqrtf(sum / (float)hidden + eps);
+  TOut* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<TOut>(in[i] * scale * weight[i]);
+}
+
+TGE_API int tge_rmsnorm(const float* x, const float* weight, const int* rows, void* out, int out_is_bf16,
+                        int out_rows, int src_rows, int hidden, float eps, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(out_rows >= 0 && hidden > 0 && src_rows >= 0, "rmsnorm: bad sizes rows=%d hidden=%d", out_rows, hidden);
+  TGE_REQUIRE(eps > 0.0f, "rmsnorm: eps must be positive");
+  if (out_rows == 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : 256;
+  if (out_is_bf16)
+    rmsnorm_kernel<__nv_bfloat16><<<out_rows, threads, 0, stream>>>(x, weight, rows, (__nv_bfloat16*)out, hidden, src_rows, eps, status);
+  else
+    rmsnorm_kernel<float><<<out_rows, threads, 0, stream>>>(x, weight, rows, (float*)out, hidden, src_rows, eps, status);
+  return tge_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------------------
+// x += y  (float32 stream, y in the run dtype)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void add_to_stream_kernel(float* __restrict__ x, const T* __restrict__ y, size_t count) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < count; i += stride) x[i] += to_float<T>(y[i]);
+}
+
+TGE_API int tge_add_to_stream(float* x, const void* y, int y_is_bf16, long long count, cudaStream_t stream) {
+  TGE_REQUIRE(count >= 0, "add_to_stream: negative count");
+  if (count == 0) return 0;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (y_is_bf16)
+    add_to_stream_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)y, (size_t)count);
+  else
+    add_to_stream_kernel<float><<<(int)blocks, 256, 0, stream>>>(x, (const float*)y, (size_t)count);
+  return tge_check_launch("add_to_stream");
+}
+
+// ---------------------------------------------------------------------------
+// Rotary rotation of q and k (rotate-half pairing over the first `rotary`
+// dimensions of each head) fused with the store of k and v into their pages.
+//   lo' = lo*cos - hi*sin ; hi' = lo*sin + hi*cos      (float32)
+// q is rotated in place inside the fused qkv rows; k is rotated on its way into
+// the cache, v is copied.  A page is [kv_heads, page_size, head_dim].
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ cos_table,
+                                     const float* __restrict__ sin_table, int table_rows,
+                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                     const int* __restrict__ block_table, int max_pages, T* __restrict__ k_pages,
+                                     T* __restrict__ v_pages, int num_pages, int page_size, int heads, int kv_heads,
+                                     int head_dim, int rotary, int store_kv, int* status) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  T* row = qkv + (size_t)t * row_stride;
+  const int half = rotary / 2;
+  const bool rotate = half > 0;
+  if (rotate && (pos < 0 || pos >= table_rows)) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+    return;
+  }
+  const float* cs = cos_table + (size_t)pos * half;
+  const float* sn = sin_table + (size_t)pos * half;
+  // queries, in place
+  if (rotate) {
+    for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+      const int h = i / half, d = i - h * half;
+      T* v = row + (size_t)h * head_dim;
+      const float lo = to_float<T>(v[d]), hi = to_float<T>(v[d + half]);
+      const float c = cs[d], s = sn[d];
+      v[d] = from_float<T>(lo * c - hi * s);
+      v[d + half] = from_float<T>(lo * s + hi * c);
+    }
+  }
+  if (!store_kv) return;
+  const int seq = seq_of_token[t];
+  const int page = block_table[(size_t)seq * max_pages + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+    return;
+  }
+  const int slot = pos % page_size;
+  const T* k_row = row + (size_t)heads * head_dim;
+  const T* v_row = k_row + (size_t)kv_heads * head_dim;
+  for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
+    const int h = i / head_dim, d = i - h * head_dim;
+    const size_t dst = (((size_t)page * kv_heads + h) * page_size + slot) * head_dim + d;
+    float kv;
+    if (d < half) {
+      const float lo = to_float<T>(k_row[i]), hi = to_float<T>(k_row[i + half]);
+      kv = lo * cs[d] - hi * sn[d];
+    } else if (d < rotary) {
+      const float lo = to_float<T>(k_row[i - half]), hi = to_float<T>(k_row[i]);
+      kv = lo * sn[d - half] + hi * cs[d - half];
+    } else {
+      kv = to_float<T>(k_row[i]);
+    }
+    k_pages[dst] = from_float<T>(kv);
+    v_pages[dst] = v_row[i];
+  }
+}
+
+TGE_API int tge_rope_kv_store(void* qkv, int is_bf16, int row_stride, const float* cos_table, const float* sin_table,
+                              int table_rows, const int* positions, const int* seq_of_token, const int* block_table,
+                              int max_pages, void* k_pages, void* v_pages, int num_pages, int page_size, int tokens,
+                              int heads, int kv_heads, int head_dim, int rotary, int store_kv, int* status,
+                              cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads >= 0 && head_dim > 0, "rope_kv_store: bad sizes");
+  TGE_REQUIRE(rotary >= 0 && rotary <= head_dim && rotary % 2 == 0,
+              "rope_kv_store: rotary width %d must be even and at most head_dim %d", rotary, head_dim);
+  TGE_REQUIRE(!store_kv || (page_size > 0 && max_pages > 0 && num_pages > 0), "rope_kv_store: bad page geometry");
+  TGE_REQUIRE(row_stride >= (heads + (store_kv ? 2 * kv_heads : 0)) * head_dim, "rope_kv_store: row stride %d too small", row_stride);
+  if (tokens == 0) return 0;
+  if (is_bf16)
+    rope_kv_store_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+        (__nv_bfloat16*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table,
+        max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim,
+        rotary, store_kv, status);
+  else
+    rope_kv_store_kernel<float><<<tokens, 256, 0, stream>>>(
+        (float*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table, max_pages,
+        (float*)k_pages, (float*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, rotary, store_kv, status);
+  return tge_check_launch("rope_kv_store");
+}

@@ -1,0 +1,515 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: out = x . w^T (+ epilogue).
+//
+// Shape of the kernel (one persistent block per SM, 192 threads):
+//   warp 0     one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
+//              of a 128-row weight tile and a BN-row activation tile per k-block
+//              of 64 into a ring of shared-memory stages;
+//   warp 1     allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN,
+//              K=16, float32 accumulators in tensor memory) and commits each
+//              stage back to the loader and each finished tile to the epilogue;
+//   warps 2-5  read the accumulator with tcgen05.ld (one 32-lane quarter each) and
+//              apply the epilogue, while the MMA warp already fills the second
+//              accumulator buffer with the next tile.
+// The weight rows are the M side of the instruction ("swap-AB"): a decode step
+// with 1..64 tokens still fills all 128 lanes with useful rows and streams each
+// weight byte exactly once; the token tile BN is 16..256.  Narrow outputs with
+// few tiles are additionally cut along k; the partial sums go to a float32
+// scratch buffer and a second kernel adds them in split order and applies the
+// epilogue, so the result does not depend on which block ran when.
+//
+// Epilogues: +bias -> run dtype; +bias -> float32; += into the float32 residual
+// stream; SiLU(gate)*up over interleaved weight rows (row 2i = gate_i, 2i+1 =
+// up_i), exchanged between neighbouring lanes.  Formulas as in gemm_simt.cu.
+//
+// Every wait on an mbarrier is bounded: after about two seconds a waiter sets
+// TGE_STATUS_WAIT_TIMEOUT in the status word, all roles leave their loops, the
+// loader waits (bounded) for its copies in flight, tensor memory is freed and
+// the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+enum GemmEpilogue : int { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_SWIGLU = 3 };
+
+namespace {
+
+constexpr int BM = 128;                  // weight rows per tile = tensor-memory lanes
+constexpr int BK = 64;                   // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int MAX_STAGES = 8;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_LIMIT = 227 * 1024;
+
+struct GemmParams {
+  int n_w, m_tok, K;
+  int bn, stages, splits;
+  int k_blocks, tiles_w, tiles_t;
+  int epilogue;
+  int acc_cols;        // tensor-memory columns allocated (power of two >= 32)
+  const float* bias;
+  void* out;
+  long long ldo;
+  float* partial;
+  int* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  return t;
+}
+
+// Bounded wait.  Returns false when it gave up or when another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer() - start > 2000000000ull) {
+        *abort_flag = 1;
+        atomicOr(status, TGE_STATUS_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major, bf16 in, f32 out
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 lanes x 16 consecutive columns of 32-bit accumulators
+__device__ __forceinline__ void tc_load16(uint32_t taddr, uint32_t r[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte
+// swizzle, 8-row groups 1024 bytes apart, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+  desc |= (uint64_t)1 << 16;                         // leading byte offset (unused for swizzled K-major)
+  desc |= (uint64_t)(1024 >> 4) << 32;               // stride byte offset between 8-row groups
+  desc |= (uint64_t)1 << 46;                         // descriptor version
+  desc |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+  return desc;
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+// ---- the kernel ------------------------------------------------------------
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  // stages first (1024-byte aligned for the swizzle), barriers after them
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t b_stage_bytes = (uint32_t)p.bn * BK * 2;
+  const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
+  const uint32_t bars = base + (uint32_t)p.stages * stage_bytes;
+  // barrier layout: full[stages], empty[stages], tmem_full[2], tmem_empty[2], then tmem base, abort flag
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (p.stages + s); };
+  auto tfull_bar = [&](int s) { return bars + 8u * (2 * p.stages + s); };
+  auto tempty_bar = [&](int s) { return bars + 8u * (2 * p.stages + 2 + s); };
+  const uint32_t tmem_slot = bars + 8u * (2 * p.stages + 4);
+  unsigned char* generic_base = smem_raw + (base - raw);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(generic_base + (size_t)p.stages * stage_bytes + 8u * (2 * p.stages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"((uint32_t)p.acc_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int total_work = p.tiles_w * p.tiles_t * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------ TMA loader ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+        const int split = work % p.splits;
+        const int rest = work / p.splits;
+        const int tile_t = rest % p.tiles_t, tile_w = rest / p.tiles_t;
+        const int kb_begin = (int)((long long)split * p.k_blocks / p.splits);
+        const int kb_end = (int)((long long)(split + 1) * p.k_blocks / p.splits);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
+          const uint32_t a_dst = base + (uint32_t)stage * stage_bytes;
+          mbar_expect_tx(full_bar(stage), stage_bytes);
+          tma_load_2d(a_dst, &map_w, full_bar(stage), kb * BK, tile_w * BM);
+          tma_load_2d(a_dst + A_STAGE_BYTES, &map_x, full_bar(stage), kb * BK, tile_t * p.bn);
+          ++issued;
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // wait (bounded) for the copies already issued, newest phase of every stage used
+        const int used = issued < p.stages ? issued : p.stages;
+        for (int back = 1; back <= used; ++back) {
+          int s = stage - back;
+          uint32_t ph = phase;
+          if (s < 0) { s += p.stages; ph ^= 1u; }
+          const unsigned long long start = global_timer();
+          while (!mbar_try_wait(full_bar(s), ph) && global_timer() - start < 100000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+        const int split = work % p.splits;
+        const int kb_begin = (int)((long long)split * p.k_blocks / p.splits);
+        const int kb_end = (int)((long long)(split + 1) * p.k_blocks / p.splits);
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.bn);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = base + (uint32_t)stage * stage_bytes;
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t desc_a = make_smem_desc(a_addr + k * UMMA_K * 2);
+            const uint64_t desc_b = make_smem_desc(b_addr + k * UMMA_K * 2);
+            tc_mma(d_tmem, desc_a, desc_b, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    const int quarter = warp & 3;            // tensor-memory lanes this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+      const int split = work % p.splits;
+      const int rest = work / p.splits;
+      const int tile_t = rest % p.tiles_t, tile_w = rest / p.tiles_t;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int n = tile_w * BM + quarter * 32 + lane;          // weight row = output feature
+      const bool n_ok = n < p.n_w;
+      const float bias = (p.bias && n_ok && p.splits == 1) ? p.bias[n] : 0.0f;
+      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+        uint32_t r[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.bn + c0);
+        tc_load16(taddr, r);
+        const int m0 = tile_t * p.bn + c0;
+        if (m0 >= p.m_tok) continue;                              // uniform over the warp
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + j;
+          float v = __uint_as_float(r[j]) + bias;
+          if (p.splits > 1) {
+            if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
+          } else if (p.epilogue == GEMM_SWIGLU) {
+            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+            if (n_ok && m < p.m_tok && (lane & 1) == 0)
+              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, other));
+          } else if (n_ok && m < p.m_tok) {
+            if (p.epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+            else if (p.epilogue == GEMM_STORE_F32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] += v;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)p.acc_cols) : "memory");
+  }
+}
+
+// Adds the k-splits in split order and applies the epilogue.
+__global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const float* __restrict__ bias, void* out,
+                                       long long ldo, int m_tok, int n_w, int splits, int epilogue) {
+  const size_t plane = (size_t)m_tok * n_w;
+  if (epilogue == GEMM_SWIGLU) {
+    const size_t count = plane / 2;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+      const int m = (int)(i / (n_w / 2)), c = (int)(i % (n_w / 2));
+      float g = 0.0f, u = 0.0f;
+      for (int s = 0; s < splits; ++s) {
+        const float2 v = *reinterpret_cast<const float2*>(partial + s * plane + (size_t)m * n_w + 2 * c);
+        g += v.x;
+        u += v.y;
+      }
+      if (bias) { g += bias[2 * c]; u += bias[2 * c + 1]; }
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + c] = __float2bfloat16_rn(silu_mul(g, u));
+    }
+    return;
+  }
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < plane; i += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / n_w), n = (int)(i % n_w);
+    float v = 0.0f;
+    for (int s = 0; s < splits; ++s) v += partial[s * plane + i];
+    if (bias) v += bias[n];
+    if (epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
+    else if (epilogue == GEMM_STORE_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+    else reinterpret_cast<float*>(out)[(size_t)m * ldo + n] += v;
+  }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// rows x K bf16 matrix, row stride `ld` elements; box = box_rows x 64 elements, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows,
+             CUtensorMapL2promotion promo) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    tge_set_error("gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+    return -3;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    tge_set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d (rows=%lld K=%lld ld=%lld box=%d)", (int)rc,
+                  rows, K, ld, box_rows);
+    return -3;
+  }
+  return 0;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 1;
+  }
+  return count;
+}
+
+struct Plan {
+  int bn, stages, splits;
+};
+
+Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int force_splits) {
+  Plan plan;
+  const int sms = sm_count();
+  const int tiles_w = (N + BM - 1) / BM;
+  int bn;
+  if (force_bn > 0) bn = force_bn;
+  else if (M <= 16) bn = 16;
+  else if (M <= 32) bn = 32;
+  else if (M <= 64) bn = 64;
+  else if (M <= 128) bn = 128;
+  else {
+    // fewer, fuller waves win: compare the time of both tilings in units of "128 columns on one SM"
+    const long long t256 = (long long)tiles_w * ((M + 255) / 256);
+    const long long t128 = (long long)tiles_w * ((M + 127) / 128);
+    const long long cost256 = (t256 + sms - 1) / sms * 2;
+    const long long cost128 = (t128 + sms - 1) / sms;
+    bn = cost128 < cost256 ? 128 : 256;
+  }
+  plan.bn = bn;
+  const int stage_bytes = A_STAGE_BYTES + bn * BK * 2;
+  int stages = (SMEM_LIMIT - 2048) / stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  const int k_blocks = (K + BK - 1) / BK;
+  if (stages > k_blocks) stages = k_blocks < 2 ? 2 : k_blocks;
+  plan.stages = stages;
+  const long long tiles = (long long)tiles_w * ((M + bn - 1) / bn);
+  int splits = 1;
+  if (force_splits > 0) splits = force_splits;
+  else if (tiles * 2 <= sms && k_blocks >= 8) {
+    splits = (int)((sms + tiles - 1) / tiles);
+    if (splits > k_blocks / 4) splits = k_blocks / 4;
+    if (splits > 16) splits = 16;
+  }
+  if (splits > k_blocks) splits = k_blocks;
+  while (splits > 1 && (long long)splits * M * N > scratch_floats) --splits;
+  if (splits < 1) splits = 1;
+  plan.splits = splits;
+  return plan;
+}
+
+}  // namespace
+
+// How many float32 of scratch the product would like (0 when it will not split along k).
+TGE_API long long tge_gemm_tcgen05_scratch_floats(int M, int N, int K) {
+  Plan plan = make_plan(M, N, K, (long long)1 << 60, 0, 0);
+  return plan.splits > 1 ? (long long)plan.splits * M * N : 0;
+}
+
+// x [M, K] bf16 (row stride ldx), w [N, K] bf16 (row stride ldw); bias float32 [N] or null;
+// out per epilogue (row stride ldo elements).  scratch: float32 buffer of scratch_floats
+// elements for split-k partial sums (may be null: no split).  force_bn / force_splits: 0 = automatic.
+// Returns 1 (and touches nothing) when the shape cannot go through TMA: K not a multiple of 8,
+// misaligned pointers or strides.  The caller then uses the CUDA-core product.
+TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                             long long ldo, int M, int N, int K, int epilogue, float* scratch,
+                             long long scratch_floats, int force_bn, int force_splits, int* status,
+                             cudaStream_t stream) {
+  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_SWIGLU, "gemm: unknown epilogue %d", epilogue);
+  TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
+  TGE_REQUIRE(force_bn == 0 || (force_bn % 16 == 0 && force_bn >= 16 && force_bn <= 256), "gemm: token tile %d must be a multiple of 16 in [16, 256]", force_bn);
+  TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
+  if (M == 0) return 0;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)w % 16 != 0) return 1;
+  if (scratch == nullptr) scratch_floats = 0;
+  const Plan plan = make_plan(M, N, K, scratch_floats, force_bn, force_splits);
+  TGE_REQUIRE(plan.splits == 1 || (long long)plan.splits * M * N <= scratch_floats,
+              "gemm_tcgen05: %d k-splits need %lld floats of scratch, have %lld", plan.splits,
+              (long long)plan.splits * M * N, scratch_floats);
+
+  CUtensorMap map_w, map_x;
+  int rc = make_map(&map_w, w, N, K, ldw, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  if (rc != 0) return rc;
+  rc = make_map(&map_x, x, M, K, ldx, plan.bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+  if (rc != 0) return rc;
+
+  GemmParams p;
+  p.n_w = N; p.m_tok = M; p.K = K;
+  p.bn = plan.bn; p.stages = plan.stages; p.splits = plan.splits;
+  p.k_blocks = (K + BK - 1) / BK;
+  p.tiles_w = (N + BM - 1) / BM;
+  p.tiles_t = (M + plan.bn - 1) / plan.bn;
+  p.epilogue = epilogue;
+  int cols = 32;
+  while (cols < 2 * plan.bn) cols *= 2;
+  p.acc_cols = cols;
+  p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
+
+  const size_t smem = 1024 + (size_t)plan.stages * (A_STAGE_BYTES + plan.bn * BK * 2) + 8 * (2 * plan.stages + 4) + 16;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    if (err != cudaSuccess) {
+      tge_set_error("gemm_tcgen05: cannot reserve shared memory: %s", cudaGetErrorString(err));
+      return -2;
+    }
+    configured = SMEM_LIMIT;
+  }
+  const long long total = (long long)p.tiles_w * p.tiles_t * p.splits;
+  const int grid = (int)(total < sm_count() ? total : sm_count());
+  gemm_tcgen05_kernel<<<grid, NUM_THREADS, smem, stream>>>(map_w, map_x, p);
+  rc = tge_check_launch("gemm_tcgen05");
+  if (rc != 0) return rc;
+  if (plan.splits > 1) {
+    const long long count = epilogue == GEMM_SWIGLU ? (long long)M * N / 2 : (long long)M * N;
+    long long blocks = (count + 255) / 256;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
+    splitk_epilogue_kernel<<<(int)blocks, 256, 0, stream>>>(scratch, bias, out, ldo, M, N, plan.splits, epilogue);
+    return tge_check_launch("splitk_epilogue");
+  }
+  return 0;
+}

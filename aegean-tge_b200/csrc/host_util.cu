@@ -1,0 +1,29 @@
+// Host-side error plumbing shared by every library built from this folder.
+// An entry point that refuses its arguments stores a message here and returns
+// a negative code; the Python binding raises it.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[768] = "";
+
+void tge_set_error(const char* fmt, ...) {
+  va_list args;
+  va_start(args, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, args);
+  va_end(args);
+}
+
+int tge_check_launch(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    tge_set_error("%s: launch failed: %s", what, cudaGetErrorString(err));
+    return -2;
+  }
+  return 0;
+}
+
+TGE_API const char* tge_last_error() { return g_error; }
+
+TGE_API int tge_abi_version() { return 1; }

@@ -1,0 +1,413 @@
+"""Bindings of the CUDA kernels: torch tensors in, raw pointers to the libraries.
+
+Every function here launches hand-written sm_100a code from ``csrc/`` on the
+current CUDA stream.  There is no CPU path and no library attention or model
+code behind any of them: if the libraries cannot be built or loaded, the
+first call raises.  Tensors are checked (device, dtype, contiguity) before a
+pointer leaves Python.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .csrc import build as _build
+
+GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32, GEMM_SWIGLU = 0, 1, 2, 3
+STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a page id outside the pool",
+               4: "a row index outside the batch", 8: "a bounded device-side wait gave up"}
+
+_c_int, _c_ll, _c_float, _c_ptr = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    """A kernel entry point refused its arguments or a launch failed."""
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel recorded a fault in the status word (bad token, bad page, ...)."""
+
+
+# ----------------------------------------------------------------------------
+# libraries
+# ----------------------------------------------------------------------------
+_core_lib: Optional[ctypes.CDLL] = None
+_attn_libs: Dict[int, ctypes.CDLL] = {}
+
+# Set to False to send bfloat16 products through the CUDA-core kernel (for A/B checks).
+USE_TCGEN05 = os.environ.get("TGE_NO_TCGEN05", "") == ""
+# Set to False to send bfloat16 attention through the CUDA-core kernel.
+USE_MMA_ATTENTION = os.environ.get("TGE_NO_MMA_ATTENTION", "") == ""
+
+
+def _declare(lib: ctypes.CDLL, name: str, argtypes) -> None:
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = _c_int
+
+
+def core() -> ctypes.CDLL:
+    global _core_lib
+    if _core_lib is None:
+        path = _build.build_core()
+        lib = ctypes.CDLL(path)
+        lib.tge_last_error.restype = ctypes.c_char_p
+        _declare(lib, "tge_embedding", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_rmsnorm", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                      _c_ptr, _c_ptr])
+        _declare(lib, "tge_add_to_stream", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr])
+        _declare(lib, "tge_rope_kv_store", [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                                            _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_gemm_simt", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
+                                        _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_gemm_tcgen05", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
+                                           _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ptr])
+        lib.tge_gemm_tcgen05_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
+        lib.tge_gemm_tcgen05_scratch_floats.restype = _c_ll
+        _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
+                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                             _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_sample", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
+        _core_lib = lib
+    return _core_lib
+
+
+def attention_lib(head_dim: int) -> ctypes.CDLL:
+    if head_dim not in _attn_libs:
+        path = _build.build_attention(head_dim)
+        lib = ctypes.CDLL(path)
+        lib.tge_last_error.restype = ctypes.c_char_p
+        _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
+                                            _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
+                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr])
+        lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
+        lib.tge_attention_mma_scratch_floats.restype = _c_ll
+        if lib.tge_attention_mma_head_dim() != head_dim:
+            raise KernelError(f"{path} was built for another head size")
+        _attn_libs[head_dim] = lib
+    return _attn_libs[head_dim]
+
+
+def mma_attention_supports(head_dim: int, heads: int, kv_heads: int, page_size: int) -> bool:
+    return (head_dim % 16 == 0 and 16 <= head_dim <= 256 and heads % kv_heads == 0
+            and heads // kv_heads <= 64 and 64 % page_size == 0)
+
+
+def loaded_libraries() -> Tuple[str, ...]:
+    names = []
+    if _core_lib is not None:
+        names.append(_core_lib._name)
+    names.extend(lib._name for lib in _attn_libs.values())
+    return tuple(names)
+
+
+def _check(rc: int, lib: ctypes.CDLL) -> None:
+    if rc < 0:
+        raise KernelError(lib.tge_last_error().decode("utf-8", "replace"))
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _want(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (this engine has no CPU path)")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _rows_2d(t: torch.Tensor, name: str) -> int:
+    """Row stride (elements) of a 2-D tensor whose rows are dense."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be 2-D with dense rows, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+_FLOAT = (torch.float32, torch.bfloat16)
+
+# ----------------------------------------------------------------------------
+# status word and scratch
+# ----------------------------------------------------------------------------
+_status: Dict[int, torch.Tensor] = {}
+_scratch: Dict[int, torch.Tensor] = {}
+
+
+def status_word(device: Optional[torch.device] = None) -> torch.Tensor:
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if index not in _status:
+        _status[index] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{index}")
+    return _status[index]
+
+
+def check_status() -> None:
+    """Reads the status word (synchronises) and raises if a kernel recorded a fault."""
+    word = status_word()
+    value = int(word.item())
+    if value:
+        word.zero_()
+        what = [text for bit, text in STATUS_BITS.items() if value & bit]
+        raise DeviceStatusError("a kernel met " + " and ".join(what or [f"status {value}"]))
+
+
+def scratch_floats(count: int) -> torch.Tensor:
+    """A float32 scratch buffer of at least ``count`` elements, reused between calls."""
+    index = torch.cuda.current_device()
+    have = _scratch.get(index)
+    if have is None or have.numel() < count:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("scratch memory must be sized before a CUDA graph is captured "
+                              f"(need {count} floats, have {0 if have is None else have.numel()})")
+        size = max(count, 1 << 22, 0 if have is None else 2 * have.numel())
+        _scratch[index] = torch.empty(size, dtype=torch.float32, device=f"cuda:{index}")
+    return _scratch[index]
+
+
+# ----------------------------------------------------------------------------
+# kernels
+# ----------------------------------------------------------------------------
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, :] = float32(table[ids[t], :])"""
+    _want(table, "embedding table", _FLOAT)
+    _want(ids, "token ids", torch.int32)
+    vocab, hidden = table.shape
+    tokens = ids.numel()
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    _want(out, "embedding output", torch.float32)
+    lib = core()
+    _check(lib.tge_embedding(table.data_ptr(), int(table.dtype == torch.bfloat16), ids.data_ptr(), out.data_ptr(),
+                             tokens, hidden, vocab, status_word().data_ptr(), _stream()), lib)
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of float32 rows (optionally gathered by ``rows``) into ``out_dtype``."""
+    _want(x, "norm input", torch.float32)
+    _want(weight, "norm weight", torch.float32)
+    src_rows, hidden = x.shape
+    if weight.numel() != hidden:
+        raise KernelError(f"norm weight has {weight.numel()} elements for rows of {hidden}")
+    out_rows = src_rows if rows is None else rows.numel()
+    if rows is not None:
+        _want(rows, "norm row index", torch.int32)
+    if out is None:
+        out = torch.empty((out_rows, hidden), dtype=out_dtype, device=x.device)
+    _want(out, "norm output", _FLOAT)
+    lib = core()
+    _check(lib.tge_rmsnorm(x.data_ptr(), weight.data_ptr(), _ptr(rows), out.data_ptr(),
+                           int(out.dtype == torch.bfloat16), out_rows, src_rows, hidden, float(eps),
+                           status_word().data_ptr(), _stream()), lib)
+    return out
+
+
+def add_to_stream(x: torch.Tensor, y: torch.Tensor) -> None:
+    """x (float32) += y (run dtype), same shape."""
+    _want(x, "stream", torch.float32)
+    _want(y, "addend", _FLOAT)
+    if x.shape != y.shape:
+        raise KernelError(f"add_to_stream: shapes differ, {tuple(x.shape)} and {tuple(y.shape)}")
+    lib = core()
+    _check(lib.tge_add_to_stream(x.data_ptr(), y.data_ptr(), int(y.dtype == torch.bfloat16), x.numel(), _stream()), lib)
+
+
+def rope_kv_store(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary: int,
+                  positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
+                  k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], heads: int, kv_heads: int,
+                  head_dim: int) -> None:
+    """Rotates q (in place) and k, and stores k and v into their pages.
+
+    qkv: [T, >= (heads + 2*kv_heads) * head_dim].  cos/sin: float32 [positions, rotary/2]
+    (None with rotary == 0: no rotation).  Pages: [num_pages, kv_heads, page_size, head_dim];
+    None: nothing is stored (a layer that reads another layer's cache).
+    """
+    _want(qkv, "qkv", _FLOAT, contiguous=False)
+    stride = _rows_2d(qkv, "qkv")
+    tokens = qkv.shape[0]
+    store = k_pages is not None
+    if rotary > 0:
+        _want(cos, "cos table", torch.float32)
+        _want(sin, "sin table", torch.float32)
+        if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != rotary // 2:
+            raise KernelError(f"rotary tables must be [positions, {rotary // 2}], got {tuple(cos.shape)}")
+    _want(positions, "positions", torch.int32)
+    _want(seq_of_token, "seq_of_token", torch.int32)
+    num_pages = page_size = max_pages = 0
+    if store:
+        _want(k_pages, "k pages", qkv.dtype)
+        _want(v_pages, "v pages", qkv.dtype)
+        _want(block_table, "block table", torch.int32)
+        if k_pages.shape != v_pages.shape or k_pages.dim() != 4 or k_pages.shape[1] != kv_heads or k_pages.shape[3] != head_dim:
+            raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {head_dim}], got {tuple(k_pages.shape)}")
+        num_pages, _, page_size, _ = k_pages.shape
+        max_pages = block_table.shape[1]
+    lib = core()
+    _check(lib.tge_rope_kv_store(qkv.data_ptr(), int(qkv.dtype == torch.bfloat16), stride, _ptr(cos), _ptr(sin),
+                                 0 if cos is None else cos.shape[0], positions.data_ptr(), seq_of_token.data_ptr(),
+                                 _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages), num_pages, page_size,
+                                 tokens, heads, kv_heads if store else 0, head_dim, rotary, int(store),
+                                 status_word().data_ptr(), _stream()), lib)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
+           out: Optional[torch.Tensor] = None, force_simt: bool = False, force_bn: int = 0,
+           force_splits: int = 0) -> torch.Tensor:
+    """out = x . w^T with an epilogue.
+
+    x [M, K] and w [N, K] in the run dtype; bias float32 [N] or None.
+    GEMM_STORE: out [M, N] run dtype.  GEMM_STORE_F32: out [M, N] float32.
+    GEMM_ADD_F32: ``out`` (float32 [M, N], required) += product.
+    GEMM_SWIGLU: w rows interleaved (gate_i, up_i); out [M, N/2] run dtype.
+    bfloat16 goes to the tcgen05 kernel when the shape allows TMA, else (and all of
+    float32) to the CUDA-core kernel.
+    """
+    _want(x, "linear input", _FLOAT, contiguous=False)
+    _want(w, "linear weight", x.dtype, contiguous=False)
+    ldx, ldw = _rows_2d(x, "linear input"), _rows_2d(w, "linear weight")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: input has {K} columns, weight has {w.shape[1]}")
+    if bias is not None:
+        _want(bias, "linear bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError(f"linear: bias has {bias.numel()} elements for {N} rows")
+    if epilogue == GEMM_ADD_F32:
+        if out is None:
+            raise KernelError("linear: the residual epilogue needs the stream as `out`")
+        want_shape, want_dtype = (M, N), torch.float32
+    elif epilogue == GEMM_STORE_F32:
+        want_shape, want_dtype = (M, N), torch.float32
+    elif epilogue == GEMM_SWIGLU:
+        want_shape, want_dtype = (M, N // 2), x.dtype
+    elif epilogue == GEMM_STORE:
+        want_shape, want_dtype = (M, N), x.dtype
+    else:
+        raise KernelError(f"linear: unknown epilogue {epilogue}")
+    if out is None:
+        out = torch.empty(want_shape, dtype=want_dtype, device=x.device)
+    _want(out, "linear output", want_dtype, contiguous=False)
+    if tuple(out.shape) != want_shape:
+        raise KernelError(f"linear: output must be {want_shape}, got {tuple(out.shape)}")
+    ldo = _rows_2d(out, "linear output")
+    lib = core()
+    if x.dtype == torch.bfloat16 and USE_TCGEN05 and not force_simt:
+        need = lib.tge_gemm_tcgen05_scratch_floats(M, N, K) if force_splits == 0 else force_splits * M * N
+        scratch = scratch_floats(need) if need > 0 else None
+        rc = lib.tge_gemm_tcgen05(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
+                                  epilogue, _ptr(scratch), 0 if scratch is None else scratch.numel(), force_bn,
+                                  force_splits, status_word().data_ptr(), _stream())
+        _check(rc, lib)
+        if rc == 0:
+            return out
+    _check(lib.tge_gemm_simt(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
+                             int(x.dtype == torch.bfloat16), epilogue, _stream()), lib)
+    return out
+
+
+def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+              q_start: torch.Tensor, start_pos: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+              num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int, kv_heads: int, head_dim: int,
+              scale: float, window: int = 0, split_tokens: int = 0, out: Optional[torch.Tensor] = None,
+              force_simt: bool = False) -> torch.Tensor:
+    """Paged causal attention of a flat batch of portions.
+
+    q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
+    pages [num_pages, kv_heads, page_size, head_dim] already hold the keys and values of
+    every position up to each portion's last token.  Returns [T, heads*head_dim].
+    ``split_tokens`` > 0 cuts the keys into runs of that many positions (a multiple of 64)
+    that are attended in parallel and merged; 0 picks a value from the batch shape.
+    """
+    _want(q, "queries", _FLOAT, contiguous=False)
+    q_stride = _rows_2d(q, "queries")
+    tokens = q.shape[0]
+    _want(k_pages, "k pages", q.dtype)
+    _want(v_pages, "v pages", q.dtype)
+    for name, t in (("block table", block_table), ("q_start", q_start), ("start_pos", start_pos),
+                    ("positions", positions), ("seq_of_token", seq_of_token)):
+        _want(t, name, torch.int32)
+    num_pages, page_kv, page_size, page_hd = k_pages.shape
+    if page_kv != kv_heads or page_hd != head_dim or v_pages.shape != k_pages.shape:
+        raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {head_dim}], got {tuple(k_pages.shape)}")
+    max_pages = block_table.shape[1]
+    if out is None:
+        out = torch.empty((tokens, heads * head_dim), dtype=q.dtype, device=q.device)
+    _want(out, "attention output", q.dtype, contiguous=False)
+    out_stride = _rows_2d(out, "attention output")
+    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt
+               and mma_attention_supports(head_dim, heads, kv_heads, page_size))
+    if use_mma:
+        lib = attention_lib(head_dim)
+        if split_tokens == 0:
+            split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, max_ctx_len, heads, kv_heads)
+        splits = 1 if split_tokens == 0 or max_ctx_len <= split_tokens else -(-max_ctx_len // split_tokens)
+        need = lib.tge_attention_mma_scratch_floats(tokens, heads, splits)
+        scratch = scratch_floats(need) if need > 0 else None
+        _check(lib.tge_attention_mma(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
+                                     block_table.data_ptr(), max_pages, num_pages, page_size, q_start.data_ptr(),
+                                     start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
+                                     max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
+                                     split_tokens, _ptr(scratch), status_word().data_ptr(), _stream()), lib)
+        return out
+    lib = core()
+    _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
+                                  block_table.data_ptr(), max_pages, num_pages, page_size, positions.data_ptr(),
+                                  seq_of_token.data_ptr(), out.data_ptr(), out_stride, tokens, heads, kv_heads,
+                                  head_dim, float(scale), window, int(q.dtype == torch.bfloat16),
+                                  status_word().data_ptr(), _stream()), lib)
+    return out
+
+
+def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int,
+                           kv_heads: int) -> int:
+    """Keys per split for the tensor-core attention: enough blocks to fill the GPU, no more.
+
+    The choice depends on the step's shape only through launch geometry; a row's value
+    differs between choices by rounding alone.
+    """
+    if max_ctx_len <= 256:
+        return 0
+    group = heads // kv_heads
+    rows = 64 if max_q_len > 1 else (16 if group <= 16 else (32 if group <= 32 else 64))
+    bq = max(rows // group, 1)
+    tiles = -(-tokens // bq) if max_q_len > 1 else num_seqs
+    blocks = tiles * kv_heads
+    target = 2 * 148
+    if blocks >= target:
+        return 0
+    want_splits = min(-(-target // blocks), -(-max_ctx_len // 128))
+    if want_splits <= 1:
+        return 0
+    split = -(-max_ctx_len // want_splits)
+    return max(128, -(-split // 64) * 64)
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 logits: arg-max where temperature <= 0, else a draw."""
+    _want(logits, "logits", torch.float32, contiguous=False)
+    stride = _rows_2d(logits, "logits")
+    rows, vocab = logits.shape
+    _want(temperature, "temperature", torch.float32)
+    _want(uniform, "uniform draws", torch.float32)
+    if temperature.numel() != rows or uniform.numel() != rows:
+        raise KernelError("sample: one temperature and one uniform draw per row")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _want(out, "sampled ids", torch.int32)
+    lib = core()
+    _check(lib.tge_sample(logits.data_ptr(), stride, temperature.data_ptr(), uniform.data_ptr(), out.data_ptr(), rows,
+                          vocab, _stream()), lib)
+    return out

@@ -1,0 +1,22 @@
+"""Arrangements of a mixer and a feed-forward around the residual stream."""
+from __future__ import annotations
+
+import torch
+
+from .base import BLOCKS, Block, LayerCache, StepContext
+
+
+@BLOCKS.register("pre_norm")
+class PreNormBlock(Block):
+    """x += mixer(norm1(x)); x += ffn(norm2(x)).
+
+    The stream ``x`` is float32 and is never itself normalised: each norm's
+    output feeds the part and the part's output is added back
+    (src/models/qwen2.cpp:2055, :2099-2105, :2118).
+    """
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+        h = self.mixer_norm.forward(x)
+        self.mixer.forward_add(h, x, ctx, cache)
+        h = self.ffn_norm.forward(x)
+        self.feed_forward.forward_add(h, x, ctx)

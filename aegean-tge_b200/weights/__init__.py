@@ -1,0 +1,8 @@
+"""Checkpoint reading, binding by name, and the random-weights mode."""
+from .loader import WeightError, check_against_manifest, load_checkpoint, load_tensors, write_model_folder
+from .random_init import fill_random, parse_dtype, write_random_model
+from .safetensors_io import ModelFiles, SafetensorsFile, WeightFileError, write_safetensors
+
+__all__ = ["WeightError", "check_against_manifest", "load_checkpoint", "load_tensors", "write_model_folder",
+           "fill_random", "parse_dtype", "write_random_model", "ModelFiles", "SafetensorsFile", "WeightFileError",
+           "write_safetensors"]
