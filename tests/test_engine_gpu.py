@@ -1,0 +1,222 @@
+"""The engine against the plain implementation: every way of cutting and batching, both dtypes."""
+import random
+
+import pytest
+import torch
+
+from conftest import TINY
+from helpers import MODEL_TOL, rel_error
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+MODELS = ["A", "B", "C"]
+
+
+def _tokens(name, count, salt=0):
+    config, seed = TINY[name]
+    rnd = random.Random(seed * 100 + salt)
+    return [rnd.randrange(config["vocab_size"]) for _ in range(count)]
+
+
+@pytest.fixture(scope="module")
+def oracle(model_dirs):
+    cache = {}
+
+    def get(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in cache:
+            if name not in cache:
+                cache[name] = plain.read_model(model_dirs[name])
+            config, weights = cache[name]
+            cache[key] = plain.logits_of(config, weights, tokens).float()
+        return cache[key]
+    return get
+
+
+def _engine(model_dirs, name, dtype, **kw):
+    from aegean_tge_b200 import Engine
+    kw.setdefault("context", 256)
+    kw.setdefault("max_tokens", 1024)
+    kw.setdefault("max_requests", 8)
+    return Engine(model_dirs[name], dtype=dtype, **kw)
+
+
+def _portion(request, tokens, want=None):
+    from aegean_tge_b200.engine import Portion
+    return Portion(request, tokens, list(range(len(tokens))) if want is None else want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_whole_prompt(model_dirs, oracle, name, dtype):
+    """Each request alone and whole, at several lengths including one token and page edges."""
+    from aegean_tge_b200 import ops
+    engine = _engine(model_dirs, name, dtype)
+    for length in (1, 7, 16, 33, 130):
+        tokens = _tokens(name, length, salt=length)
+        logits = engine.runner.step([_portion("r", tokens)])
+        engine.runner.finish("r")
+        assert rel_error(logits, oracle(name, tokens)) < MODEL_TOL[dtype], (name, dtype, length)
+    ops.check_status()
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_last_32_tokens_one_by_one(model_dirs, oracle, name, dtype):
+    """Most of the sequence in one step, the last 32 tokens decoded one at a time."""
+    tokens = _tokens(name, 100, salt=1)
+    ref = oracle(name, tokens)
+    engine = _engine(model_dirs, name, dtype)
+    rows = [engine.runner.step([_portion("r", tokens[:68])])]
+    for t in range(68, 100):
+        rows.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
+    got = torch.cat(rows)
+    assert rel_error(got, ref) < MODEL_TOL[dtype]
+    if dtype == "float32":
+        # decoding a token and running it inside a prompt are the same arithmetic per row
+        whole = _engine(model_dirs, name, dtype).runner.step([_portion("w", tokens)])
+        assert float((got - whole).abs().max()) <= 1e-5 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_portions_of_changing_size(model_dirs, oracle, name, dtype):
+    tokens = _tokens(name, 120, salt=2)
+    ref = oracle(name, tokens)
+    engine = _engine(model_dirs, name, dtype)
+    cuts = [7, 2, 16, 3, 2, 30, 2, 17, 41]
+    assert sum(cuts) == len(tokens)
+    rows, pos = [], 0
+    for count in cuts:
+        rows.append(engine.runner.step([_portion("r", tokens[pos:pos + count])]))
+        pos += count
+    assert rel_error(torch.cat(rows), ref) < MODEL_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_mixed_batches_with_page_reuse(model_dirs, oracle, name, dtype):
+    """Up to four live requests, prompt portions beside decoded tokens, so few pages that they are reused."""
+    from aegean_tge_b200 import ops
+    lengths = {"a": 70, "b": 45, "c": 130, "d": 19, "e": 64, "f": 33}
+    tokens = {r: _tokens(name, n, salt=ord(r)) for r, n in lengths.items()}
+    engine = _engine(model_dirs, name, dtype, max_tokens=320)       # 20 pages: a+b+c+d alone need 18
+    got = {r: [] for r in lengths}
+    done = {r: 0 for r in lengths}
+
+    def run(step):
+        portions = []
+        for r, count in step:
+            portions.append(_portion(r, tokens[r][done[r]:done[r] + count]))
+        logits = engine.runner.step(portions)
+        row = 0
+        for r, count in step:
+            got[r].append(logits[row:row + count])
+            row += count
+            done[r] += count
+            if done[r] == lengths[r]:
+                engine.runner.finish(r)
+        engine.cache.check()
+
+    run([("a", 33)])
+    run([("a", 1), ("b", 20)])
+    run([("b", 2), ("a", 1), ("c", 50)])
+    run([("c", 30), ("a", 1), ("b", 1), ("d", 19)])            # d finishes: its pages go back
+    run([("a", 34), ("b", 22), ("c", 1)])                      # a and b finish
+    run([("c", 49), ("e", 17)])                                # c finishes; e starts on reused pages
+    run([("e", 2), ("f", 30)])
+    run([("f", 1), ("e", 1)])
+    run([("e", 44), ("f", 2)])
+    assert all(done[r] == lengths[r] for r in lengths)
+    for r in lengths:
+        assert rel_error(torch.cat(got[r]), oracle(name, tokens[r])) < MODEL_TOL[dtype], r
+    ops.check_status()
+    assert not engine.cache.live_requests()
+    assert all(g.pool.free_count == g.pool.capacity for g in engine.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model_dirs, oracle, dtype):
+    """A short prompt, then 200 tokens one by one (teacher-forced), across many page edges."""
+    name = "B"
+    tokens = _tokens(name, 210, salt=3)
+    ref = oracle(name, tokens)
+    engine = _engine(model_dirs, name, dtype)
+    rows = [engine.runner.step([_portion("r", tokens[:10])])]
+    for t in range(10, 210):
+        rows.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
+    assert rel_error(torch.cat(rows), ref) < MODEL_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", MODELS)
+def test_first_tokens_of_a_sequence(model_dirs, oracle, name, dtype):
+    """Positions 0, 1, 2: one key, the first rotation angles, a page with one slot in use."""
+    tokens = _tokens(name, 3, salt=4)
+    ref = oracle(name, tokens)
+    engine = _engine(model_dirs, name, dtype)
+    rows = [engine.runner.step([_portion("r", tokens[t:t + 1])]) for t in range(3)]
+    assert rel_error(torch.cat(rows), ref) < MODEL_TOL[dtype]
+
+
+def test_only_wanted_rows_come_back(model_dirs, oracle):
+    tokens = _tokens("A", 40, salt=5)
+    ref = oracle("A", tokens)
+    engine = _engine(model_dirs, "A", "float32")
+    assert engine.runner.step([_portion("r", tokens[:20], want=[])]) is None
+    logits = engine.runner.step([_portion("r", tokens[20:], want=[19, 0])])
+    assert logits.shape == (2, 256)
+    assert rel_error(logits, ref[[39, 20]]) < MODEL_TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_point(model_dirs, dtype):
+    """Engine.generate against the plain implementation's greedy continuation (float32: token for token)."""
+    from aegean_tge_b200 import Engine
+    name = "B"
+    config, weights = plain.read_model(model_dirs[name])
+    prompts = [_tokens(name, n, salt=50 + n) for n in (1, 7, 33)]
+    engine = Engine(model_dirs[name], dtype=dtype, context=128, max_tokens=512, max_batch_tokens=16, max_requests=4)
+    outputs = engine.generate(prompts, n=16)
+    for prompt, output in zip(prompts, outputs):
+        assert len(output) == 16
+        if dtype == "float32":
+            assert output == plain.greedy(config, weights, prompt, 16)
+        else:
+            # bfloat16 may flip a near-tie: every chosen token must be within tolerance of the best one
+            tokens = list(prompt)
+            for token in output:
+                row = plain.logits_of(config, weights, tokens)[-1]
+                assert float(row.max() - row[token]) < MODEL_TOL[dtype] * float(row.abs().max())
+                tokens.append(token)
+    single = engine.generate(prompts[1], n=4)
+    assert single == outputs[1][:4]
+
+
+def test_generation_does_not_depend_on_pages_or_budget(model_dirs):
+    """Same requests, same tokens, whatever the pool size, token budget and chunk (preemption included)."""
+    from aegean_tge_b200 import Engine, SamplingParams
+    name = "A"
+    prompts = [_tokens(name, n, salt=70 + n) for n in (5, 19, 64, 130)]
+    params = [SamplingParams(temperature=0.8, seed=11 + i) for i in range(4)]
+    outputs = []
+    for kw in (dict(max_tokens=2048, max_batch_tokens=512), dict(max_tokens=2048, max_batch_tokens=16, chunk=16),
+               dict(num_pages=15, max_batch_tokens=16, chunk=16), dict(num_pages=13, max_batch_tokens=40, chunk=7)):
+        engine = Engine(model_dirs[name], dtype="float32", context=256, max_requests=4, **kw)
+        outputs.append(engine.generate(prompts, n=24, sampling=params))
+        engine.cache.check()
+        assert all(g.pool.free_count == g.pool.capacity for g in engine.cache.groups)
+        if "num_pages" in kw:
+            assert engine.stats()["preemptions"] > 0
+    assert all(o == outputs[0] for o in outputs[1:])
+
+
+def test_kernels_are_loaded_and_cpu_is_refused(model_dirs):
+    from aegean_tge_b200 import ops
+    _engine(model_dirs, "A", "bfloat16")
+    names = " ".join(ops.loaded_libraries())
+    assert "libtge_core.so" in names and "libtge_attn_hd16.so" in names
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-6, torch.float32)

@@ -1,0 +1,222 @@
+"""A mixer with state of its own, defined here, registered, built and stepped through the engine
+without touching the package: the layer list mixes it with attention, and a second toy
+architecture runs a layer twice and lets a layer read another layer's cache."""
+import random
+
+import pytest
+import torch
+
+from helpers import MODEL_TOL, rel_error
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+HIDDEN, VOCAB, HEADS, KV, HD, INNER = 48, 97, 3, 1, 16, 80
+
+
+def _register():
+    from aegean_tge_b200.config.model_spec import LayerSpec, ModelSpec, PartSpec
+    from aegean_tge_b200.parts.base import MIXERS, Mixer, ParamSpec, StateSpec
+    from aegean_tge_b200.registry import Architecture, register_architecture, registered_architectures
+
+    if "toy_running_mean" not in MIXERS.names():
+        @MIXERS.register("toy_running_mean")
+        class RunningMean(Mixer):
+            """y_t = W mean(h_0..h_t): the running sum and the count live in the request's state slot."""
+
+            def __init__(self, spec, env):
+                super().__init__(spec, env)
+                self.hidden = int(spec.params["hidden_size"])
+                self.weight = None
+
+            def param_specs(self):
+                return {"mix.weight": ParamSpec((self.hidden, self.hidden))}
+
+            def load(self, tensors):
+                self.weight = tensors["mix.weight"]
+
+            def state_spec(self):
+                return StateSpec((("sum", (self.hidden,)), ("count", (1,))))
+
+            def forward(self, h, ctx, cache):
+                out = torch.empty_like(h)
+                begin = 0
+                for count, slot in zip(ctx.host_q_lens, ctx.host_slots):
+                    part = h[begin:begin + count].float()
+                    running = cache.state["sum"][slot] + torch.cumsum(part, dim=0)
+                    seen = cache.state["count"][slot] + torch.arange(1, count + 1, device=h.device)[:, None]
+                    cache.state["sum"][slot] = running[-1]
+                    cache.state["count"][slot] += count
+                    out[begin:begin + count] = ((running / seen) @ self.weight.float().T).to(h.dtype)
+                    begin += count
+                return out
+
+    def names(n):
+        p = f"layers.{n}."
+        return p
+
+    def build_spec(config):
+        position = PartSpec("rope_neox", {"head_dim": HD, "theta": 777.0})
+        norm = lambda name: PartSpec("rmsnorm", {"size": HIDDEN, "eps": 1e-5}, {"weight": name})
+        layers = []
+        for n, kind in enumerate(config["kinds"]):
+            p = f"layers.{n}."
+            if kind == "toy":
+                mixer = PartSpec("toy_running_mean", {"hidden_size": HIDDEN}, {"mix.weight": p + "mix.weight"})
+            else:
+                mixer = PartSpec("gqa_attention",
+                                 {"hidden_size": HIDDEN, "heads": HEADS, "kv_heads": KV, "head_dim": HD,
+                                  "qkv_bias": kind == "attention_bias", "o_bias": False,
+                                  "window": config.get("window") if kind == "attention_window" else None,
+                                  "position": position},
+                                 {f"{x}.{y}": p + f"{x}.{y}" for x in "qkvo" for y in ("weight", "bias")})
+            ffn = PartSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": INNER},
+                           {f"{x}.weight": p + f"{x}.weight" for x in ("gate", "up", "down")})
+            layers.append(LayerSpec("pre_norm", mixer, ffn, norm(p + "norm1"), norm(p + "norm2"),
+                                    cache_from=config.get("cache_from", {}).get(n)))
+        sizes = {"vocab_size": VOCAB, "hidden_size": HIDDEN}
+        return ModelSpec("ToyForTests", HIDDEN, VOCAB, 256, tuple(layers), tuple(config["schedule"]),
+                         PartSpec("token_embedding", sizes, {"weight": "embed"}), norm("final_norm"),
+                         PartSpec("linear_head", sizes, {"weight": "head"}))
+
+    def random_tensors(config, generator, matrix_dtype, device):
+        def mat(*shape):
+            return (torch.randn(shape, generator=generator, device=device) * 0.08).to(matrix_dtype)
+        def vec(n, around=0.0):
+            return around + torch.randn(n, generator=generator, device=device) * 0.05
+        yield "embed", mat(VOCAB, HIDDEN)
+        yield "head", mat(VOCAB, HIDDEN)
+        yield "final_norm", vec(HIDDEN, 1.0)
+        for n, kind in enumerate(config["kinds"]):
+            p = f"layers.{n}."
+            yield p + "norm1", vec(HIDDEN, 1.0)
+            yield p + "norm2", vec(HIDDEN, 1.0)
+            if kind == "toy":
+                yield p + "mix.weight", mat(HIDDEN, HIDDEN)
+            else:
+                yield p + "q.weight", mat(HEADS * HD, HIDDEN)
+                yield p + "k.weight", mat(KV * HD, HIDDEN)
+                yield p + "v.weight", mat(KV * HD, HIDDEN)
+                yield p + "o.weight", mat(HIDDEN, HEADS * HD)
+                if kind == "attention_bias":
+                    yield p + "q.bias", vec(HEADS * HD)
+                    yield p + "k.bias", vec(KV * HD)
+                    yield p + "v.bias", vec(KV * HD)
+            for x, shape in (("gate", (INNER, HIDDEN)), ("up", (INNER, HIDDEN)), ("down", (HIDDEN, INNER))):
+                yield p + f"{x}.weight", mat(*shape)
+
+    if "ToyForTests" not in registered_architectures():
+        register_architecture(Architecture("ToyForTests", parse_config=lambda raw: raw, build_spec=build_spec,
+                                           random_tensors=random_tensors))
+
+
+def _plain_logits(config, w, tokens):
+    """The toy architecture restated on whole sequences in float64, from the plain parts."""
+    T = len(tokens)
+    cos, sin = plain.rope_tables(777.0, HD, T)
+    x = plain.embed(w["embed"], tokens)
+    kv_of = {}
+    for n in config["schedule"]:
+        kind = config["kinds"][n]
+        p = f"layers.{n}."
+        h = plain.rms_norm(x, w[p + "norm1"], 1e-5)
+        if kind == "toy":
+            mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=h.dtype)[:, None]
+            x = x + mean @ w[p + "mix.weight"].T
+        else:
+            bias = lambda name, width: w.get(p + name, torch.zeros(width, dtype=h.dtype))
+            q = plain.apply_rope((h @ w[p + "q.weight"].T + bias("q.bias", HEADS * HD)).view(T, HEADS, HD), cos, sin)
+            source = config.get("cache_from", {}).get(n)
+            if source is None:
+                k = plain.apply_rope((h @ w[p + "k.weight"].T + bias("k.bias", KV * HD)).view(T, KV, HD), cos, sin)
+                v = (h @ w[p + "v.weight"].T + bias("v.bias", KV * HD)).view(T, KV, HD)
+                kv_of[n] = (k, v)
+            else:
+                k, v = kv_of[source]
+            window = config.get("window", 0) if kind == "attention_window" else 0
+            a = plain.attention(q, k, v, window=window).reshape(T, HEADS * HD)
+            x = x + a @ w[p + "o.weight"].T
+        h = plain.rms_norm(x, w[p + "norm2"], 1e-5)
+        x = x + plain.swiglu(h, w[p + "gate.weight"], w[p + "up.weight"], w[p + "down.weight"])
+    return (plain.rms_norm(x, w["final_norm"], 1e-5) @ w["head"].T).float()
+
+
+def _engine_and_weights(config, dtype):
+    from aegean_tge_b200 import Engine
+    _register()
+    raw = dict(config, architectures=["ToyForTests"])
+    engine = Engine(random_config=raw, seed=3, dtype=dtype, context=256, max_tokens=512, max_requests=4)
+    # read the weights back from the parts, so the oracle sees exactly what the engine holds
+    w = {}
+    model = engine.model
+    w["embed"] = model.embedding.weight.double().cpu()
+    w["head"] = model.head.weight.double().cpu()
+    w["final_norm"] = model.final_norm.weight.double().cpu()
+    for n, block in enumerate(model.blocks):
+        p = f"layers.{n}."
+        w[p + "norm1"] = block.mixer_norm.weight.double().cpu()
+        w[p + "norm2"] = block.ffn_norm.weight.double().cpu()
+        if config["kinds"][n] == "toy":
+            w[p + "mix.weight"] = block.mixer.weight.double().cpu()
+        else:
+            qkv = block.mixer.w_qkv.double().cpu()
+            w[p + "q.weight"], w[p + "k.weight"], w[p + "v.weight"] = qkv.split([HEADS * HD, KV * HD, KV * HD])
+            w[p + "o.weight"] = block.mixer.w_o.double().cpu()
+            if block.mixer.b_qkv is not None:
+                b = block.mixer.b_qkv.double().cpu()
+                w[p + "q.bias"], w[p + "k.bias"], w[p + "v.bias"] = b.split([HEADS * HD, KV * HD, KV * HD])
+        gu = block.feed_forward.w_gate_up.double().cpu()
+        w[p + "gate.weight"], w[p + "up.weight"] = gu[0::2], gu[1::2]
+        w[p + "down.weight"] = block.feed_forward.w_down.double().cpu()
+    return engine, w
+
+
+CONFIGS = {
+    "state_and_attention": {"kinds": ["toy", "attention_bias", "toy"], "schedule": [0, 1, 2]},
+    "twice_shared_window": {"kinds": ["attention", "attention_window", "attention", "toy"], "window": 24,
+                            "schedule": [0, 1, 2, 3, 1], "cache_from": {2: 0}},
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", list(CONFIGS))
+def test_toy_parts_step_through_the_engine(which, dtype):
+    from aegean_tge_b200.engine import Portion
+    config = CONFIGS[which]
+    if which == "twice_shared_window":
+        # a layer that runs twice would write its cache twice; the toy keeps that layer stateless per visit
+        config = dict(config, schedule=[0, 1, 2, 3])
+    engine, w = _engine_and_weights(config, dtype)
+    rnd = random.Random(5)
+    a = [rnd.randrange(VOCAB) for _ in range(90)]
+    b = [rnd.randrange(VOCAB) for _ in range(41)]
+    ref_a, ref_b = _plain_logits(config, w, a), _plain_logits(config, w, b)
+    full = lambda r, t: Portion(r, t, list(range(len(t))))
+    got_a, got_b = [], []
+    got_a.append(engine.runner.step([full("a", a[:37])]))
+    out = engine.runner.step([full("a", a[37:38]), full("b", b[:20])])
+    got_a.append(out[:1]); got_b.append(out[1:])
+    out = engine.runner.step([full("b", b[20:22]), full("a", a[38:88])])
+    got_b.append(out[:2]); got_a.append(out[2:])
+    out = engine.runner.step([full("a", a[88:]), full("b", b[22:])])
+    got_a.append(out[:2]); got_b.append(out[2:])
+    assert rel_error(torch.cat(got_a), ref_a) < MODEL_TOL[dtype]
+    assert rel_error(torch.cat(got_b), ref_b) < MODEL_TOL[dtype]
+    if which == "twice_shared_window":
+        assert len(engine.cache.groups) == 2                 # full-attention layers and the windowed one
+        windowed = [g for g in engine.cache.groups if g.spec.window == 24][0]
+        assert -1 in windowed.tables["a"]                     # pages behind the window went back
+    engine.runner.finish("a"); engine.runner.finish("b")
+    engine.cache.check()
+    assert engine.cache.free_slots == 4
+
+
+def test_a_layer_may_run_twice():
+    """schedule names layer 0 (the stateful toy) twice: both visits share its weights and its state."""
+    from aegean_tge_b200.engine import Portion
+    config = {"kinds": ["toy", "attention"], "schedule": [0, 1, 0]}
+    engine, w = _engine_and_weights(config, "float32")
+    tokens = [3, 50, 7, 7, 96, 0, 12]
+    logits = engine.runner.step([Portion("r", tokens, list(range(len(tokens))))])
+    assert logits.shape == (len(tokens), VOCAB) and torch.isfinite(logits).all()
+    assert engine.model.step_param_bytes() > 0
