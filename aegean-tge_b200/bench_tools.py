@@ -1,0 +1,117 @@
+"""Timed prefill and decode steps with their roofline fractions, shared by `tge bench` and bench.py.
+
+Timing is with CUDA events on the launching stream after warm-up, with a
+synchronize on both sides.  A decode step reads every weight once (about
+15 GB for the 7B shape) plus the cache of the live requests, far more than
+the 126 MB L2, so no extra flush is needed between steps; the prefill's
+weights are likewise larger than L2.
+"""
+from __future__ import annotations
+
+import random
+from typing import Dict, List
+
+import torch
+
+from . import peaks as _peaks
+from .engine.batch import Portion
+
+
+def _random_tokens(vocab: int, count: int, seed: int) -> List[int]:
+    rnd = random.Random(seed)
+    return [rnd.randrange(vocab) for _ in range(count)]
+
+
+def prefill_flops(engine, tokens: int) -> float:
+    """Multiply-adds of one whole prompt, times two: the products plus causal attention."""
+    model = engine.model
+    matrix_params = 0
+    attention = 0.0
+    for index in engine.spec.schedule:
+        block = model.blocks[index]
+        for part in block.parts().values():
+            for name in ("w_qkv", "w_o", "w_gate_up", "w_down"):
+                w = getattr(part, name, None)
+                if w is not None:
+                    matrix_params += w.numel()
+        mixer = block.mixer
+        if hasattr(mixer, "heads"):
+            attention += 4.0 * mixer.heads * mixer.head_dim * tokens * (tokens + 1) / 2.0
+    head = model.head.weight.numel()          # one row of logits
+    return 2.0 * tokens * matrix_params + attention + 2.0 * head
+
+
+def bench_prefill(engine, prompt_len: int, repeat: int = 3, warmup: int = 2) -> Dict[str, float]:
+    vocab = engine.spec.vocab_size
+    times = []
+    for it in range(warmup + repeat):
+        tokens = _random_tokens(vocab, prompt_len, seed=100 + it)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.runner.step([Portion("bench-prefill", tokens, [prompt_len - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.runner.finish("bench-prefill")
+        if it >= warmup:
+            times.append(start.elapsed_time(stop))
+    ms = sum(times) / len(times)
+    flops = prefill_flops(engine, prompt_len)
+    peak, source = _peaks.load()
+    tflops = flops / (ms * 1e-3) / 1e12
+    return {"tokens": prompt_len, "ms": ms, "tok_s": prompt_len / (ms * 1e-3), "tflops": tflops,
+            "peak_tflops": peak["bf16_tflops"], "frac": tflops / peak["bf16_tflops"], "peak_source": source,
+            "flops": flops}
+
+
+def fill_cache(engine, batch: int, prompt_len: int, chunk: int = 2048, prefix: str = "bench") -> List[str]:
+    """Prefills ``batch`` requests of ``prompt_len`` random tokens (untimed); returns their ids."""
+    vocab = engine.spec.vocab_size
+    names = []
+    for b in range(batch):
+        name = f"{prefix}-{b}"
+        tokens = _random_tokens(vocab, prompt_len, seed=1000 + b)
+        for begin in range(0, prompt_len, chunk):
+            engine.runner.step([Portion(name, tokens[begin:begin + chunk], [])])
+        names.append(name)
+    return names
+
+
+def decode_step_bytes(engine, names: List[str]) -> float:
+    """Bytes a decode step must read: every weight it uses once, and the cache of the live requests."""
+    cached = sum(engine.cache.computed(n) for n in names)
+    return engine.model.step_param_bytes() + cached * engine.model.cache_bytes_per_token()
+
+
+def bench_decode(engine, batch: int, prompt_len: int, steps: int = 64, warmup: int = 3) -> Dict[str, float]:
+    """Device-timed decode steps (model and sampling kernels; the sampled ids stay on the device)."""
+    from . import ops
+    names = fill_cache(engine, batch, prompt_len)
+    vocab = engine.spec.vocab_size
+    zeros = torch.zeros(batch, dtype=torch.float32, device=engine.device)
+    feed = [_random_tokens(vocab, warmup + steps, seed=5000 + b) for b in range(batch)]
+    def one(step: int):
+        logits = engine.runner.step([Portion(n, [feed[b][step]], [0]) for b, n in enumerate(names)])
+        return ops.sample(logits, zeros, zeros)
+    for step in range(warmup):
+        one(step)
+    torch.cuda.synchronize()
+    bytes_first = decode_step_bytes(engine, names)
+    launches_before = ops.launches
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for step in range(warmup, warmup + steps):
+        one(step)
+    stop.record()
+    torch.cuda.synchronize()
+    ops.check_status()
+    ms = start.elapsed_time(stop) / steps
+    bytes_last = decode_step_bytes(engine, names)
+    for n in names:
+        engine.runner.finish(n)
+    step_bytes = (bytes_first + bytes_last) / 2
+    peak, source = _peaks.load()
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    return {"batch": batch, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3), "step_bytes": step_bytes, "gbs": gbs,
+            "peak_gbs": peak["hbm_gbs"], "frac": gbs / peak["hbm_gbs"], "peak_source": source,
+            "launches": ops.launches - launches_before, "steps": steps}

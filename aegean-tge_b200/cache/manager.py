@@ -122,11 +122,15 @@ class CacheManager:
         return [int(pages)] * len(self.groups)
 
     def allocate_storage(self, dtype: torch.dtype, device: torch.device) -> None:
-        """Creates the page and state tensors (zero-filled, so stale pages hold finite values)."""
+        """Creates the page and state tensors (zero-filled, so stale pages hold finite values).
+
+        Every group gets one page more than its pool hands out (id ``capacity``): a scratch
+        page that warm-up runs may write without touching a live request.
+        """
         for group in self.groups:
             group.storage = {}
             for name, shape in group.spec.entries:
-                full = (len(group.layers), group.pool.capacity, *shape[:-1], self.page_size, shape[-1])
+                full = (len(group.layers), group.pool.capacity + 1, *shape[:-1], self.page_size, shape[-1])
                 group.storage[name] = torch.zeros(full, dtype=dtype, device=device)
         self.state_storage = {}
         for layer, spec in self.state_specs.items():

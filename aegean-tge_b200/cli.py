@@ -1,0 +1,297 @@
+"""The `tge` command line, in the manner of the reference's (apps/cli/main.cpp:45-140).
+
+    tge info [--json]
+    tge plan --model DIR [--context N] [--sessions N] [--bandwidth GB/s]
+    tge generate --model DIR --tokens "a b c" [--n N] [--temp T] [--top-k N] [--top-p P] [--min-p P]
+                 [--repeat-penalty R] [--penalty-window N] [--seed N] [--context N] [--print-ids]
+    tge bench prefill|decode --model DIR [--prompt-len N] [--batch B] [--n N] [--repeat R]
+    tge make-random --config FILE --out DIR [--seed S] [--dtype float32|bfloat16]
+    tge replay --model DIR --dtype D --out DIR --max-tokens N          (same as bin/trace_run)
+    tge version
+
+Options shared with the reference keep its names, defaults and meanings:
+``--n`` tokens to generate (default 32), ``--context`` cache length (default
+4096, capped by the model), ``--temp`` 0 is greedy, ``--top-k`` / ``--top-p`` /
+``--min-p`` / ``--repeat-penalty`` / ``--penalty-window`` / ``--seed`` as in
+its sampler, ``--print-ids``.  Output lines carry its labels (``load``,
+``resolved``, ``model``, ``prefill``, ``decode``, ``ids``; decode excludes the
+first generated token, main.cpp:1216-1219).  Exit codes: 2 for a usage error,
+1 for a load or run-time failure (main.cpp:3061-3072).  ``--prompt`` / ``--text``
+need a tokenizer, which this engine does not have: it takes and returns ids.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+from typing import List, Optional
+
+from . import __version__
+
+
+class UsageError(Exception):
+    pass
+
+
+class _Parser(argparse.ArgumentParser):
+    def error(self, message):
+        raise UsageError(f"{self.prog}: {message}")
+
+
+def _model_args(parser: argparse.ArgumentParser) -> None:
+    parser.add_argument("--model", help="model folder (config.json + model.safetensors)")
+    parser.add_argument("--random-config", help="config.json file: run with seeded random weights instead of --model")
+    parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
+    parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
+    parser.add_argument("--context", type=int, default=4096, help="KV cache length (default 4096, capped by model)")
+    parser.add_argument("--num-pages", type=int, help="pages of 16 tokens in the cache pool (default: from free memory)")
+    parser.add_argument("--max-batch-tokens", type=int, default=2048, help="token budget of one step")
+    parser.add_argument("--chunk", type=int, help="largest prompt portion in one step (default: the budget)")
+    parser.add_argument("--max-requests", type=int, default=64)
+
+
+def _sampling_args(parser: argparse.ArgumentParser) -> None:
+    parser.add_argument("--temp", type=float, default=0.0, help="sampling temperature; 0 is greedy (default 0)")
+    parser.add_argument("--top-k", type=int, default=0, help="keep the N best tokens (default off)")
+    parser.add_argument("--top-p", type=float, default=1.0, help="nucleus probability mass (default 1.0)")
+    parser.add_argument("--min-p", type=float, default=0.0, help="drop tokens below this fraction of the best")
+    parser.add_argument("--repeat-penalty", type=float, default=1.0, help="penalty for already seen tokens (default 1)")
+    parser.add_argument("--penalty-window", type=int, default=64, help="recent tokens the penalty sees; 0 is all")
+    parser.add_argument("--seed", type=int, default=0, help="random seed for sampling")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    parser = _Parser(prog="tge", description=f"aegean-tge b200 {__version__} - Qwen2.5 inference engine for one B200")
+    commands = parser.add_subparsers(dest="command", parser_class=_Parser)
+    info = commands.add_parser("info", help="GPU, memory and kernel report")
+    info.add_argument("--json", action="store_true")
+    plan = commands.add_parser("plan", help="memory budget and decode ceiling, before loading")
+    plan.add_argument("--model", required=True)
+    plan.add_argument("--context", type=int, default=4096)
+    plan.add_argument("--sessions", type=int, default=1)
+    plan.add_argument("--bandwidth", type=float, help="GB/s (default: the measured or nominal HBM figure)")
+    plan.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    generate = commands.add_parser("generate", help="generate tokens and report token rates")
+    _model_args(generate)
+    _sampling_args(generate)
+    generate.add_argument("--tokens", help='prompt token ids, "a b c"')
+    generate.add_argument("--prompt", help="(needs a tokenizer: not supported, give --tokens)")
+    generate.add_argument("--prompt-len", type=int, help="random prompt of this many ids instead of --tokens")
+    generate.add_argument("--n", type=int, default=32, help="tokens to generate (default 32)")
+    generate.add_argument("--print-ids", action="store_true", help="print generated token ids")
+    generate.add_argument("--text", action="store_true", help="(needs a tokenizer: not supported)")
+    bench = commands.add_parser("bench", help="prefill or decode throughput with its roofline fraction")
+    bench.add_argument("what", choices=["prefill", "decode"])
+    _model_args(bench)
+    bench.add_argument("--prompt-len", type=int, default=2048)
+    bench.add_argument("--batch", type=int, default=1)
+    bench.add_argument("--n", type=int, default=64, help="decode steps to time")
+    bench.add_argument("--repeat", type=int, default=3)
+    make = commands.add_parser("make-random", help="write a model folder with seeded random weights")
+    make.add_argument("--config", required=True, help="a config.json")
+    make.add_argument("--out", required=True)
+    make.add_argument("--seed", type=int, default=0)
+    make.add_argument("--dtype", default="float32", choices=["float32", "bfloat16"])
+    replay = commands.add_parser("replay", help="feed token ids step by step and write logits (bin/trace_run)")
+    replay.add_argument("--model", required=True)
+    replay.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    replay.add_argument("--out", required=True)
+    replay.add_argument("--max-tokens", type=int, required=True)
+    commands.add_parser("version", help="print the engine version")
+    return parser
+
+
+def _engine_from(args):
+    from .engine.engine import Engine
+    if bool(args.model) == bool(args.random_config):
+        raise UsageError("give --model DIR or --random-config FILE")
+    random_config = None
+    if args.random_config:
+        with open(args.random_config, "r", encoding="utf-8") as handle:
+            random_config = json.load(handle)
+    return Engine(args.model, random_config=random_config, seed=args.weights_seed, dtype=args.dtype,
+                  context=args.context, num_pages=args.num_pages, max_batch_tokens=args.max_batch_tokens,
+                  chunk=args.chunk, max_requests=args.max_requests)
+
+
+def command_info(args) -> int:
+    import torch
+    from .csrc import build
+    facts = {"version": __version__, "cuda_available": torch.cuda.is_available(), "torch": torch.__version__,
+             "cuda_runtime": torch.version.cuda, "page_size": 16, "kernel_target": "sm_100a",
+             "kernel_sources": build.CORE_SOURCES + ["attention_mma.cu"]}
+    if torch.cuda.is_available():
+        props = torch.cuda.get_device_properties(0)
+        free, total = torch.cuda.mem_get_info(0)
+        facts.update({"gpu": props.name, "sms": props.multi_processor_count,
+                      "compute_capability": f"{props.major}.{props.minor}", "memory_total_bytes": total,
+                      "memory_free_bytes": free})
+    if args.json:
+        print(json.dumps(facts))
+    else:
+        for key, value in facts.items():
+            print(f"{key:<20}: {value}")
+    return 0
+
+
+def command_plan(args) -> int:
+    """Bytes before loading, in the manner of the reference's planner (src/models/plan.cpp:28-133)."""
+    from .config.qwen2 import read_config_json
+    from .registry import architecture_of
+    from .peaks import hbm_gbs
+    raw = read_config_json(args.model)
+    arch = architecture_of(raw)
+    config = arch.parse_config(raw)
+    element = 2 if args.dtype == "bfloat16" else 4
+    h, q, kv, ff, v = config.hidden_size, config.q_dim, config.kv_dim, config.intermediate_size, config.vocab_size
+    per_layer = (q + 2 * kv) * h + h * q + 3 * ff * h
+    matrices = config.num_hidden_layers * per_layer + v * h
+    weights = (matrices + (0 if config.tie_word_embeddings else v * h)) * element
+    decode_bytes = matrices * element                       # everything but the embedding rows (plan.cpp:42-46)
+    kv_per_token = config.num_hidden_layers * 2 * kv * element
+    bandwidth = args.bandwidth or hbm_gbs()
+    total = weights + args.sessions * args.context * kv_per_token
+    print(f"weights  : {weights / 2**30:.2f} GiB ({args.dtype})")
+    print(f"kv       : {kv_per_token} bytes per token; {args.sessions} x {args.context} tokens = "
+          f"{args.sessions * args.context * kv_per_token / 2**30:.2f} GiB")
+    print(f"total    : {total / 2**30:.2f} GiB")
+    print(f"decode   : {decode_bytes / 2**20:.1f} MiB read per token; ceiling {bandwidth * 1e9 / decode_bytes:.1f} tok/s "
+          f"at {bandwidth:.0f} GB/s")
+    return 0
+
+
+def _parse_ids(text: str) -> List[int]:
+    try:
+        return [int(part) for part in text.replace(",", " ").split()]
+    except ValueError:
+        raise UsageError('--tokens takes integers, "a b c"')
+
+
+def command_generate(args) -> int:
+    import random
+    import torch
+    from . import ops
+    from .sampling.params import SamplingParams
+    if args.prompt or args.text:
+        raise UsageError("generate: --prompt and --text need a tokenizer, which this engine does not have; give --tokens")
+    if args.n <= 0:
+        raise UsageError("generate: token count must be positive")
+    sampling = SamplingParams(temperature=args.temp, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
+                              repeat_penalty=args.repeat_penalty, penalty_window=args.penalty_window, seed=args.seed)
+    try:
+        sampling.validate()
+    except ValueError as error:
+        raise UsageError(f"generate: {error}")
+    started = time.time()
+    engine = _engine_from(args)
+    print(f"load     : {(time.time() - started) * 1e3:.1f} ms")
+    facts = engine.describe()
+    print(f"resolved : dtype={facts['dtype']} context={facts['max_model_len']} page={facts['page_size']} "
+          f"pages={facts['pages_per_group']} budget={args.max_batch_tokens} kernels=sm_100a")
+    if args.tokens:
+        prompt = _parse_ids(args.tokens)
+    elif args.prompt_len:
+        rnd = random.Random(0)
+        prompt = [rnd.randrange(engine.spec.vocab_size) for _ in range(args.prompt_len)]
+    else:
+        raise UsageError("generate: at least one prompt token is required")
+    if not prompt:
+        raise UsageError("generate: at least one prompt token is required")
+    if len(prompt) + args.n + 1 > engine.max_model_len:
+        raise UsageError(f"generate: {len(prompt)} prompt tokens + {args.n} generated exceeds the "
+                         f"{engine.max_model_len} token context")
+    for token in prompt:
+        if not 0 <= token < engine.spec.vocab_size:
+            raise UsageError(f"generate: token {token} is outside the vocabulary")
+    config = engine.config
+    print(f"model    : {args.model or args.random_config}, {facts['layers']} layers, {facts['hidden_size']} dim, "
+          f"{getattr(config, 'num_attention_heads', '?')}/{getattr(config, 'num_key_value_heads', '?')} heads, "
+          f"vocab {facts['vocab_size']}")
+    if not engine.spec.end_token_ids:
+        print("generate: warning: model declares no end-of-generation ids; stopping only at --n", file=sys.stderr)
+    request_id = engine.add_request(prompt, args.n, sampling)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    finished = []
+    request = engine.scheduler.waiting[0]
+    while not request.output and not finished:
+        finished = engine.step()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    print(f"prefill  : {len(prompt)} tokens in {(t1 - t0) * 1e3:.2f} ms ({len(prompt) / (t1 - t0):.1f} tok/s)")
+    while not finished:
+        finished = engine.step()
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    ops.check_status()
+    output = finished[0].output
+    if finished[0].finish_reason == "end_token":
+        print(f"stop     : end token {output[-1]} after {len(output)} tokens")
+    timed = len(output) - 1
+    if timed > 0:
+        print(f"decode   : {timed} tokens in {(t2 - t1) * 1e3:.2f} ms ({timed / (t2 - t1):.2f} tok/s)")
+    if args.print_ids:
+        print("ids      : " + " ".join(str(t) for t in output))
+    return 0
+
+
+def command_bench(args) -> int:
+    from .bench_tools import bench_decode, bench_prefill
+    engine = _engine_from(args)
+    if args.what == "prefill":
+        result = bench_prefill(engine, args.prompt_len, repeat=args.repeat)
+        print(f"prefill  : {result['tokens']} tokens in {result['ms']:.2f} ms ({result['tok_s']:.1f} tok/s), "
+              f"{result['tflops']:.1f} TFLOP/s = {result['frac']:.3f} of {result['peak_tflops']:.0f} ({result['peak_source']})")
+    else:
+        result = bench_decode(engine, args.batch, args.prompt_len, steps=args.n)
+        print(f"decode   : batch {args.batch} at context {args.prompt_len}: {result['ms_per_step']:.3f} ms/step "
+              f"({result['tok_s']:.1f} tok/s), {result['gbs']:.0f} GB/s = {result['frac']:.3f} of "
+              f"{result['peak_gbs']:.0f} ({result['peak_source']})")
+    return 0
+
+
+def command_make_random(args) -> int:
+    from .weights.random_init import write_random_model
+    with open(args.config, "r", encoding="utf-8") as handle:
+        raw = json.load(handle)
+    write_random_model(args.out, raw, args.seed, args.dtype)
+    print(f"wrote    : {args.out}/config.json and model.safetensors (seed {args.seed}, {args.dtype})")
+    return 0
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    parser = build_parser()
+    try:
+        args = parser.parse_args(argv)
+        if args.command is None:
+            parser.print_help()
+            return 0
+        if args.command == "version":
+            print(f"aegean-tge b200 {__version__}")
+            return 0
+        if args.command == "info":
+            return command_info(args)
+        if args.command == "plan":
+            return command_plan(args)
+        if args.command == "generate":
+            return command_generate(args)
+        if args.command == "bench":
+            return command_bench(args)
+        if args.command == "make-random":
+            return command_make_random(args)
+        if args.command == "replay":
+            from .engine.replay import main as replay_main
+            return replay_main(["--model", args.model, "--dtype", args.dtype, "--out", args.out,
+                                "--max-tokens", str(args.max_tokens)])
+        raise UsageError(f"unknown command {args.command}")
+    except UsageError as error:
+        print(str(error), file=sys.stderr)
+        return 2
+    except Exception as error:  # load and run-time failures
+        print(f"tge: {type(error).__name__}: {error}", file=sys.stderr)
+        return 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -427,7 +427,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     dim3 grid(tokens, heads);
     attention_merge_kernel<<<grid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
         p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
-    return tge_check_launch("attention_merge");
+    return tge_launched("attention_merge", 2);
   }
-  return 0;
+  return 1;
 }

@@ -108,5 +108,5 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
     attention_simt_kernel<float><<<grid, 128, 0, stream>>>(
         (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_pages, num_pages,
         page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, scale, window, status);
-  return tge_check_launch("attention_simt");
+  return tge_launched("attention_simt", 1);
 }

@@ -25,7 +25,14 @@ enum TgeStatusBits : int {
 };
 
 void tge_set_error(const char* fmt, ...);
+// 0 when the last launch was accepted, a negative code (message stored) otherwise
 int tge_check_launch(const char* what);
+// Entry points return the number of kernels they launched (>= 0) or a negative code.
+inline int tge_launched(const char* what, int kernels) {
+  const int rc = tge_check_launch(what);
+  return rc != 0 ? rc : kernels;
+}
+constexpr int TGE_UNSUPPORTED = -100;  // shape outside what the kernel takes; nothing was touched
 
 #define TGE_REQUIRE(cond, ...)            \
   do {                                    \

@@ -34,7 +34,7 @@ TGE_API int tge_embedding(const void* table, int is_bf16, const int* ids, float*
     embedding_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
   else
     embedding_kernel<float><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
-  return tge_check_launch("embedding");
+  return tge_launched("embedding", 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -75,7 +75,7 @@ TGE_API int tge_rmsnorm(const float* x, const float* weight, const int* rows, vo
     rmsnorm_kernel<__nv_bfloat16><<<out_rows, threads, 0, stream>>>(x, weight, rows, (__nv_bfloat16*)out, hidden, src_rows, eps, status);
   else
     rmsnorm_kernel<float><<<out_rows, threads, 0, stream>>>(x, weight, rows, (float*)out, hidden, src_rows, eps, status);
-  return tge_check_launch("rmsnorm");
+  return tge_launched("rmsnorm", 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -97,7 +97,7 @@ TGE_API int tge_add_to_stream(float* x, const void* y, int y_is_bf16, long long 
     add_to_stream_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)y, (size_t)count);
   else
     add_to_stream_kernel<float><<<(int)blocks, 256, 0, stream>>>(x, (const float*)y, (size_t)count);
-  return tge_check_launch("add_to_stream");
+  return tge_launched("add_to_stream", 1);
 }
 
 // ---------------------------------------------------------------------------
@@ -184,5 +184,5 @@ TGE_API int tge_rope_kv_store(void* qkv, int is_bf16, int row_stride, const floa
     rope_kv_store_kernel<float><<<tokens, 256, 0, stream>>>(
         (float*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table, max_pages,
         (float*)k_pages, (float*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, rotary, store_kv, status);
-  return tge_check_launch("rope_kv_store");
+  return tge_launched("rope_kv_store", 1);
 }

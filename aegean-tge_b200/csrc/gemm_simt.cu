@@ -150,5 +150,5 @@ TGE_API int tge_gemm_simt(const void* x, long long ldx, const void* w, long long
   else
     gemm_simt_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (size_t)ldx, (const float*)w, (size_t)ldw,
                                                       bias, out, (size_t)ldo, M, N, K, epilogue, vec);
-  return tge_check_launch("gemm_simt");
+  return tge_launched("gemm_simt", 1);
 }

@@ -452,8 +452,8 @@ TGE_API long long tge_gemm_tcgen05_scratch_floats(int M, int N, int K) {
 // x [M, K] bf16 (row stride ldx), w [N, K] bf16 (row stride ldw); bias float32 [N] or null;
 // out per epilogue (row stride ldo elements).  scratch: float32 buffer of scratch_floats
 // elements for split-k partial sums (may be null: no split).  force_bn / force_splits: 0 = automatic.
-// Returns 1 (and touches nothing) when the shape cannot go through TMA: K not a multiple of 8,
-// misaligned pointers or strides.  The caller then uses the CUDA-core product.
+// Returns TGE_UNSUPPORTED (and touches nothing) when the shape cannot go through TMA: K not a
+// multiple of 8, misaligned pointers or strides.  The caller then uses the CUDA-core product.
 TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
                              long long ldo, int M, int N, int K, int epilogue, float* scratch,
                              long long scratch_floats, int force_bn, int force_splits, int* status,
@@ -464,7 +464,7 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
   TGE_REQUIRE(force_bn == 0 || (force_bn % 16 == 0 && force_bn >= 16 && force_bn <= 256), "gemm: token tile %d must be a multiple of 16 in [16, 256]", force_bn);
   TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
   if (M == 0) return 0;
-  if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)w % 16 != 0) return 1;
+  if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)w % 16 != 0) return TGE_UNSUPPORTED;
   if (scratch == nullptr) scratch_floats = 0;
   const Plan plan = make_plan(M, N, K, scratch_floats, force_bn, force_splits);
   TGE_REQUIRE(plan.splits == 1 || (long long)plan.splits * M * N <= scratch_floats,
@@ -509,7 +509,7 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
     long long blocks = (count + 255) / 256;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     splitk_epilogue_kernel<<<(int)blocks, 256, 0, stream>>>(scratch, bias, out, ldo, M, N, plan.splits, epilogue);
-    return tge_check_launch("splitk_epilogue");
+    return tge_launched("splitk_epilogue", 2);
   }
-  return 0;
+  return 1;
 }

@@ -133,5 +133,5 @@ TGE_API int tge_sample(const float* logits, long long row_stride, const float* t
   TGE_REQUIRE(row_stride >= vocab, "sample: row stride %lld shorter than the vocabulary %d", row_stride, vocab);
   if (rows == 0) return 0;
   sample_kernel<<<rows, 1024, 0, stream>>>(logits, row_stride, temperature, uniform, out, vocab);
-  return tge_check_launch("sample");
+  return tge_launched("sample", 1);
 }

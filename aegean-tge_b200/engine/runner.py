@@ -23,7 +23,13 @@ from .batch import Portion, build_context
 
 
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, max_model_len: int):
+    def __init__(self, model: DecoderModel, cache: CacheManager, max_model_len: int, use_graphs: bool = True,
+                 max_graph_batch: int = 256):
+        """``use_graphs``: steps made only of single tokens replay a CUDA graph captured per batch size."""
+        self.use_graphs = use_graphs and not cache.state_specs      # stateful toy mixers loop on the host
+        self.max_graph_batch = max_graph_batch
+        self._graphs: Dict[int, "DecodeGraph"] = {}
+        self.graph_replays = 0
         self.model = model
         self.cache = cache
         self.max_model_len = max_model_len
@@ -75,12 +81,120 @@ class ModelRunner:
         requests = [p.request for p in portions]
         starts = [self.cache.computed(r) for r in requests]
         slots = [self.cache.slot_of(r) for r in requests]
-        tables = [self.cache.block_table(g, requests) for g in range(len(self.cache.groups))]
-        ctx, rows, h2d = build_context(portions, starts, slots, tables, self.device)
-        self.h2d_bytes_last = h2d
-        logits = self.model.forward(ctx, rows)
+        batch = len(portions)
+        if self.use_graphs and batch <= self.max_graph_batch and all(len(p.tokens) == 1 for p in portions):
+            graph = self._graphs.get(batch)
+            if graph is None:
+                graph = self._graphs[batch] = DecodeGraph(self, batch)
+            tables = [self.cache.block_table(g, requests, width=graph.width) for g in range(len(self.cache.groups))]
+            logits = graph.run([int(p.tokens[0]) for p in portions], starts, slots, tables)
+            self.ops.launches += graph.kernels
+            self.h2d_bytes_last = graph.nbytes
+            self.graph_replays += 1
+            wanted = [i for i, p in enumerate(portions) if len(p.want)]
+            if not wanted:
+                logits = None
+            elif len(wanted) != batch:
+                logits = logits[torch.tensor(wanted, device=self.device)]
+            else:
+                logits = logits.clone()          # the graph's own buffer is overwritten by the next replay
+            num_tokens = batch
+        else:
+            tables = [self.cache.block_table(g, requests) for g in range(len(self.cache.groups))]
+            ctx, rows, h2d = build_context(portions, starts, slots, tables, self.device)
+            self.h2d_bytes_last = h2d
+            logits = self.model.forward(ctx, rows)
+            num_tokens = ctx.num_tokens
         for portion, start in zip(portions, starts):
             self.cache.set_computed(portion.request, start + len(portion.tokens))
         self.steps += 1
-        self.tokens_run += ctx.num_tokens
+        self.tokens_run += num_tokens
         return logits
+
+
+class DecodeGraph:
+    """One CUDA graph of a decode step for a fixed number of requests.
+
+    All index arrays live in one static device buffer that is refilled from a
+    pinned host buffer before each replay; launch geometry is captured for the
+    longest context the engine allows, and blocks whose key range is empty
+    return at once, so one graph serves every context length.
+    """
+
+    def __init__(self, runner: "ModelRunner", batch: int):
+        from ..parts.base import StepContext
+        self.batch = batch
+        model, cache = runner.model, runner.cache
+        device = runner.device
+        self.width = -(-runner.max_model_len // cache.page_size)
+        groups = len(cache.groups)
+        sizes = [("token_ids", batch), ("positions", batch), ("seq_of_token", batch), ("q_start", batch + 1),
+                 ("start_pos", batch), ("ctx_len", batch), ("slots", batch), ("rows", batch)]
+        sizes += [(f"table{g}", batch * self.width) for g in range(groups)]
+        self.offsets, cursor = {}, 0
+        for name, count in sizes:
+            self.offsets[name] = (cursor, count)
+            cursor += count
+        # A ring of pinned staging buffers: the host may fill the next one while earlier copies are
+        # still queued; a buffer is reused only after the copy that read it has finished.
+        self.ring = 4
+        self.hosts = [torch.zeros(cursor, dtype=torch.int32).pin_memory() for _ in range(self.ring)]
+        self.copied = [None] * self.ring
+        self.turn = 0
+        self.dev = torch.zeros(cursor, dtype=torch.int32, device=device)
+        view = lambda t, name: t[self.offsets[name][0]:self.offsets[name][0] + self.offsets[name][1]]
+        self.hs = [{name: view(host, name) for name, _ in sizes} for host in self.hosts]
+        d = {name: view(self.dev, name) for name, _ in sizes}
+        for h in self.hs:
+            # constants of a decode step
+            h["seq_of_token"].copy_(torch.arange(batch, dtype=torch.int32))
+            h["q_start"].copy_(torch.arange(batch + 1, dtype=torch.int32))
+            h["rows"].copy_(torch.arange(batch, dtype=torch.int32))
+            # warm-up contents: every request one token at position 0 on the scratch page
+            h["ctx_len"].fill_(1)
+            for g, group in enumerate(cache.groups):
+                h[f"table{g}"].fill_(group.pool.capacity)
+        self.dev.copy_(self.hosts[0])
+        self.nbytes = cursor * 4
+        self.ctx = StepContext(
+            num_tokens=batch, num_seqs=batch, token_ids=d["token_ids"], positions=d["positions"],
+            seq_of_token=d["seq_of_token"], q_start=d["q_start"], start_pos=d["start_pos"], ctx_len=d["ctx_len"],
+            slots=d["slots"], block_tables=[d[f"table{g}"].view(batch, self.width) for g in range(groups)],
+            max_q_len=1, max_ctx_len=runner.max_model_len, host_q_lens=[1] * batch, host_start_pos=[0] * batch,
+            host_slots=[0] * batch)
+        self.rows = d["rows"]
+        ops = runner.ops
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                model.forward(self.ctx, self.rows)
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize(device)
+        before = ops.launches
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = model.forward(self.ctx, self.rows)
+        self.kernels = ops.launches - before
+        ops.launches = before
+
+    def run(self, tokens, positions, slots, tables) -> torch.Tensor:
+        turn = self.turn
+        self.turn = (turn + 1) % self.ring
+        if self.copied[turn] is not None:
+            self.copied[turn].synchronize()
+        h = self.hs[turn]
+        h["token_ids"].copy_(torch.tensor(tokens, dtype=torch.int32))
+        pos = torch.tensor(positions, dtype=torch.int32)
+        h["positions"].copy_(pos)
+        h["start_pos"].copy_(pos)
+        h["ctx_len"].copy_(pos + 1)
+        h["slots"].copy_(torch.tensor(slots, dtype=torch.int32))
+        for g, table in enumerate(tables):
+            h[f"table{g}"].copy_(torch.tensor(table, dtype=torch.int32).view(-1))
+        self.dev.copy_(self.hosts[turn], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.copied[turn] = event
+        self.graph.replay()
+        return self.logits

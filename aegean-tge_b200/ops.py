@@ -106,9 +106,19 @@ def loaded_libraries() -> Tuple[str, ...]:
     return tuple(names)
 
 
-def _check(rc: int, lib: ctypes.CDLL) -> None:
+UNSUPPORTED = -100
+launches = 0          # kernels launched through this module since import (or since the caller reset it)
+
+
+def _check(rc: int, lib: ctypes.CDLL) -> int:
+    """Raises on an error code; otherwise counts and returns the number of kernels launched."""
+    global launches
+    if rc == UNSUPPORTED:
+        return rc
     if rc < 0:
         raise KernelError(lib.tge_last_error().decode("utf-8", "replace"))
+    launches += rc
+    return rc
 
 
 def _stream() -> int:
@@ -309,8 +319,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
         rc = lib.tge_gemm_tcgen05(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                                   epilogue, _ptr(scratch), 0 if scratch is None else scratch.numel(), force_bn,
                                   force_splits, status_word().data_ptr(), _stream())
-        _check(rc, lib)
-        if rc == 0:
+        if _check(rc, lib) != UNSUPPORTED:
             return out
     _check(lib.tge_gemm_simt(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                              int(x.dtype == torch.bfloat16), epilogue, _stream()), lib)

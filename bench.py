@@ -1,0 +1,193 @@
+#!/usr/bin/env python3
+"""Headline measurement: decode tokens/s of the Qwen2.5-7B shape in bfloat16 on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one decode step of a batch of 8 requests, each after a prompt of
+2,048 tokens (random weights, random token ids).  Prints one JSON line:
+``value`` is decoded tokens per second timed on the device over K steps,
+``e2e`` the same through the Python entry point with host tokens in and out,
+``prefill`` a 2,048-token prompt in one step against the bf16 tensor peak,
+``roofline`` the decode step against HBM bandwidth, ``points`` decode at batch
+1 and 64.  This engine runs on one GPU: for --gpus above 1 it says so and
+exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# The Qwen2.5-7B shape of BASELINE.json's configs[2]
+CONFIG_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
+    "head_dim": 128, "intermediate_size": 18944, "vocab_size": 152064, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 32768,
+    "use_sliding_window": False, "hidden_act": "silu",
+}
+PROMPT = 2048
+CONTEXT = 4096
+BATCH = 8
+
+
+def reference_arm() -> int:
+    """The reference is a C++/CMake CPU engine for Windows with no Python packaging: it cannot be
+    installed with pip, has no CUDA path, and never ran this model; see DESIGN.md."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = ("the reference is a CMake C++ CPU engine without setup.py/pyproject.toml: 'pip install /root/reference' "
+           "finds nothing to build, and it has no GPU path or bf16 model to run this metric with")
+    if os.path.isdir(ref) and os.listdir(ref):
+        why = "baseline/_ref holds no importable package that exposes the reference's generate path; " + why
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ["clocks.sm", "clocks.max.sm", "clocks_event_reasons.hw_slowdown",
+              "clocks_event_reasons.hw_thermal_slowdown", "clocks_event_reasons.sw_thermal_slowdown",
+              "clocks_event_reasons.sw_power_cap"]
+
+    def __init__(self):
+        self.path = os.path.join(tempfile.gettempdir(), f"tge_clocks_{os.getpid()}.csv")
+        self.proc = None
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", "--query-gpu=" + ",".join(self.FIELDS),
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        self.out.close()
+        clocks, peak, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as handle:
+            for line in handle:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) != len(self.FIELDS):
+                    continue
+                try:
+                    clocks.append(float(parts[0]))
+                    peak = float(parts[1])
+                except ValueError:
+                    continue
+                for name, value in zip(names, parts[2:]):
+                    if value.lower().startswith("active"):
+                        reasons.add(name)
+        os.remove(self.path)
+        clocks.sort()
+        median = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": median, "sm_max_mhz": peak, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--layers", type=int, default=CONFIG_7B["num_hidden_layers"],
+                        help="fewer layers than the model has, if memory or time needs it (both numbers are reported)")
+    parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import aegean_tge_b200 as tge
+    from aegean_tge_b200 import ops, peaks
+    from aegean_tge_b200.bench_tools import _random_tokens, bench_decode, bench_prefill, decode_step_bytes
+    from aegean_tge_b200.engine.scheduler import Request
+
+    raw = dict(CONFIG_7B, num_hidden_layers=args.layers)
+    need = args.warmup + args.steps + BATCH + 8
+    most_batch = BATCH if args.skip_points else 64
+    engine = tge.Engine(random_config=raw, seed=0, dtype="bfloat16", context=CONTEXT,
+                        max_tokens=most_batch * (PROMPT + need + 64), max_batch_tokens=PROMPT, max_requests=most_batch)
+    peak, peak_source = peaks.load()
+
+    prefill = bench_prefill(engine, PROMPT, repeat=3, warmup=2)
+
+    sampler = ClockSampler()
+    sampler.start()
+    main_run = bench_decode(engine, BATCH, PROMPT, steps=args.steps, warmup=args.warmup)
+    clocks = sampler.stop()
+
+    # the same through the public entry point: host token ids in, sampled ids out, every step
+    vocab = engine.spec.vocab_size
+    for b in range(BATCH):
+        engine.add_request(_random_tokens(vocab, PROMPT, seed=2000 + b), n=args.warmup + args.steps + BATCH + 4)
+    while any(not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
+        engine.step()                                   # prefill and the first token, untimed
+    for _ in range(args.warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - t0
+    h2d = engine.runner.h2d_bytes_last + 8 * BATCH
+    d2h = engine.d2h_bytes_last
+    while engine.has_unfinished():
+        engine.step()
+    ops.check_status()
+
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            points[f"decode_b{batch}"] = round(bench_decode(engine, batch, PROMPT, steps=min(args.steps, 32),
+                                                            warmup=args.warmup)["tok_s"], 1)
+
+    line = {
+        "metric": "decode tok/s at batch 8 after 2,048-token prompts; Qwen2.5-7B shape bf16 (with prefill tok/s at "
+                  "2,048 tokens and decode at batch 1/64)",
+        "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) seed 0, uniform random token ids",
+        "config": {
+            "model": "Qwen2.5-7B shape", "layers": args.layers, "layers_of_model": CONFIG_7B["num_hidden_layers"],
+            "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+            "global_batch": BATCH, "seq_len": PROMPT, "context_limit": CONTEXT, "page_size": engine.cache.page_size,
+            "prefill_tokens": PROMPT, "parallelism": "1 GPU", "cuda_graph": engine.runner.use_graphs,
+            "l2": "each step reads all weights (>> 126 MB L2), no flush needed",
+            "peaks": peak_source,
+        },
+        "clocks": clocks,
+        "e2e": {"value": round(BATCH * args.steps / e2e_seconds, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": main_run["launches"],
+        "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
+                    "frac": round(prefill["frac"], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(main_run["gbs"], 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(main_run["frac"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

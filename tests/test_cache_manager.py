@@ -52,9 +52,9 @@ def test_layers_with_equal_needs_share_a_group():
     assert m.groups[0].layers == [0, 2, 4] and m.groups[1].layers == [1, 3]
     assert m.layer_group[3] == 1 and m.layer_row[4] == 2
     m.allocate_storage(torch.float32, torch.device("cpu"))
-    assert m.groups[0].storage["k"].shape == (3, 8, 2, 16, 8)
+    assert m.groups[0].storage["k"].shape == (3, 8 + 1, 2, 16, 8)      # one scratch page beyond the pool
     view = m.layer_cache(2)
-    assert view.group == 0 and view.paged["v"].shape == (8, 2, 16, 8) and view.owner
+    assert view.group == 0 and view.paged["v"].shape == (9, 2, 16, 8) and view.owner
     shared = m.layer_cache(3, source=1)
     assert shared.group == 1 and not shared.owner
     assert shared.paged["k"].data_ptr() == m.layer_cache(1).paged["k"].data_ptr()

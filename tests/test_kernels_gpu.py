@@ -310,25 +310,32 @@ def test_sample_greedy_takes_the_first_maximum(ops):
 
 
 @pytest.mark.parametrize("vocab", [331, 4097, 152064])
-def test_sample_temperature_matches_the_sequential_walk(ops, vocab):
-    from plain.qwen2_plain import PlainXorShift32, sample_plain
+def test_sample_temperature_lands_where_the_draw_points(ops, vocab):
+    """The chosen index is the one whose slice of the exact (float64) cumulative distribution holds the
+    draw u.  Float32 sums over n terms are exact to about n * 2^-24 of the total, so the draw may sit
+    that far outside the chosen slice, no further; on a small vocabulary the kernel must also agree
+    with the sequential float32 walk of the reference."""
+    from plain.qwen2_plain import sample_plain
+    import numpy as np
     gen = torch.Generator().manual_seed(vocab)
     rows = 6
     logits = torch.randn(rows, vocab, generator=gen) * 2.0
     temps = [0.8, 1.0, 0.3, 2.0, 0.8, 0.05]
-    rng = PlainXorShift32(7)
-    uniforms = [float(rng.next()) for _ in range(rows)]
+    uniforms = [0.37, 0.9991, 0.0004, 0.5, 0.73, 0.11]
     ids = ops.sample(logits.to(DEV), torch.tensor(temps, device=DEV), torch.tensor(uniforms, device=DEV)).cpu().tolist()
+    slack = vocab * 2.0 ** -24
 
     class Fixed:
         def __init__(self, u): self.u = u
-        def next(self):
-            import numpy as np
-            return np.float32(self.u)
+        def next(self): return np.float32(self.u)
     for r in range(rows):
-        expected = sample_plain(logits[r].numpy(), temps[r], Fixed(uniforms[r]))
-        # the parallel prefix sums round differently from the sequential walk: allow the neighbour
-        assert abs(ids[r] - expected) <= 1, (r, ids[r], expected)
+        z = logits[r].double()
+        e = torch.exp((z - z.max()) / temps[r])
+        cdf = torch.cumsum(e, 0) / e.sum()
+        lower = float(cdf[ids[r] - 1]) if ids[r] > 0 else 0.0
+        assert lower - slack <= uniforms[r] <= float(cdf[ids[r]]) + slack, (r, ids[r], lower, float(cdf[ids[r]]))
+        if vocab <= 4097:
+            assert ids[r] == sample_plain(logits[r].numpy(), temps[r], Fixed(uniforms[r]))
 
 
 def test_sample_histogram_follows_the_distribution(ops):
