@@ -42,7 +42,7 @@ struct AttnParams {
   float* partial_ml;
   int* status;
   int q_stride, out_stride;
-  int max_pages, num_pages, page_size;
+  int max_pages, num_pages, page_size, page_shift;
   int num_seqs, total_tokens;
   int heads, kv_heads, group, bq;
   int window, split_tokens, num_splits;
@@ -88,10 +88,10 @@ __device__ __forceinline__ void load_tile(const AttnParams& p, const __nv_bfloat
     const void* src = pages;
     int bytes = 0;
     if (kpos >= lo && kpos < hi) {
-      const int page_index = kpos / p.page_size;
+      const int page_index = kpos >> p.page_shift;
       const int page = page_index < p.max_pages ? table[page_index] : -1;
       if (page >= 0 && page < p.num_pages) {
-        src = pages + (((size_t)page * p.kv_heads + kvh) * p.page_size + (kpos - page_index * p.page_size)) * HD + part * 8;
+        src = pages + ((((size_t)page * p.kv_heads + kvh) << p.page_shift) + (kpos & (p.page_size - 1))) * HD + part * 8;
         bytes = 16;
       } else {
         bad_page = true;
@@ -313,6 +313,209 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode: every portion is one token.  A block owns one (request, kv head, split)
+// and its 16 rows are the query heads of the group (padded).  The four warps
+// share each 64-position tile: warp w takes positions [16w, 16w+16) with its own
+// running maximum and sum, tiles arrive through a three-stage cp.async ring, and
+// the four states are merged through shared memory at the end, in warp order.
+// ---------------------------------------------------------------------------
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_STAGES = 3;
+constexpr int STAGE_ELEMS = 2 * BKV * ROW_ELEMS;   // K tile then V tile
+
+__global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const AttnParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int token = p.q_start[seq];
+  const int pos = p.start_pos[seq];
+
+  int lo = p.window > 0 ? max(pos - p.window + 1, 0) : 0;
+  int hi = pos + 1;
+  if (p.num_splits > 1) {
+    lo = max(lo, split * p.split_tokens);
+    hi = min(hi, (split + 1) * p.split_tokens);
+  }
+  if (lo >= hi) return;
+
+  // The page ids of this block's key range, fetched once: the copy loops then index shared memory.
+  // (The staged row is addressed like the global one, so ids before first_page are never read.)
+  int* local_table = reinterpret_cast<int*>(smem_raw + (size_t)DEC_STAGES * STAGE_ELEMS * sizeof(__nv_bfloat16));
+  const int first_page = lo >> p.page_shift, last_page = (hi - 1) >> p.page_shift;
+  for (int i = first_page + tid; i <= last_page; i += DEC_WARPS * 32)
+    local_table[i - first_page] = i < p.max_pages ? p.block_table[(size_t)seq * p.max_pages + i] : -1;
+  __syncthreads();
+  const int* table = local_table - first_page;
+
+  // Q fragments: rows are the heads of the group
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = g8 + 8 * i;
+      const bool valid = r < p.group;
+      const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * p.group + (valid ? r : 0)) * HD + kc * 16 + 2 * t4;
+      qf[kc][i] = valid ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+      qf[kc][i + 2] = valid ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+    }
+  }
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[d][e] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+
+  bool bad_page = false;
+  const int k_first = lo / BKV * BKV;
+  const int num_tiles = (hi - k_first + BKV - 1) / BKV;
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < num_tiles) {
+      load_tile<DEC_WARPS>(p, p.k_pages, table, kvh, stages + s * STAGE_ELEMS, k_first + s * BKV, lo, hi, bad_page);
+      load_tile<DEC_WARPS>(p, p.v_pages, table, kvh, stages + s * STAGE_ELEMS + BKV * ROW_ELEMS, k_first + s * BKV, lo, hi, bad_page);
+    }
+    cp_async_commit();
+  }
+  for (int it = 0; it < num_tiles; ++it) {
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncthreads();
+    {
+      const int next = it + DEC_STAGES - 1;
+      if (next < num_tiles) {
+        __nv_bfloat16* dst = stages + (next % DEC_STAGES) * STAGE_ELEMS;
+        load_tile<DEC_WARPS>(p, p.k_pages, table, kvh, dst, k_first + next * BKV, lo, hi, bad_page);
+        load_tile<DEC_WARPS>(p, p.v_pages, table, kvh, dst + BKV * ROW_ELEMS, k_first + next * BKV, lo, hi, bad_page);
+      }
+      cp_async_commit();
+    }
+    const __nv_bfloat16* tK = stages + (it % DEC_STAGES) * STAGE_ELEMS;
+    const __nv_bfloat16* tV = tK + BKV * ROW_ELEMS;
+    const int k0 = k_first + it * BKV + warp * 16;     // this warp's 16 positions
+    if (k0 >= hi || k0 + 16 <= lo) continue;            // nothing visible in this slice (warp-uniform)
+
+    float s_acc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_acc[n][e] = 0.0f;
+#pragma unroll
+    for (int kc = 0; kc < HD / 16; ++kc) {
+      const int mi = lane >> 3;
+      const int n = warp * 16 + (mi >> 1) * 8 + (lane & 7);
+      const int kofs = kc * 16 + (mi & 1) * 8;
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4(smem_u32(tK + n * ROW_ELEMS + kofs), r0, r1, r2, r3);
+      mma_bf16(s_acc[0], qf[kc], r0, r1);
+      mma_bf16(s_acc[1], qf[kc], r2, r3);
+    }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const bool row_valid = g8 + 8 * i < p.group;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kpos = k0 + n * 8 + 2 * t4 + e;
+          const bool visible = row_valid && kpos >= lo && kpos < hi;
+          const float sv = visible ? s_acc[n][2 * i + e] * p.scale_log2 : -INFINITY;
+          s_acc[n][2 * i + e] = sv;
+          mx = fmaxf(mx, sv);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[i], mx);
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+      corr[i] = exp2f(m_run[i] - m_use);
+      float sum = 0.0f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float pv = exp2f(s_acc[n][2 * i + e] - m_use);
+          s_acc[n][2 * i + e] = pv;
+          sum += pv;
+        }
+      }
+      l_run[i] = l_run[i] * corr[i] + sum;
+      m_run[i] = m_new;
+    }
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) {
+      o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
+      o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
+    }
+    uint32_t pf[4];
+    pf[0] = pack_bf16(s_acc[0][0], s_acc[0][1]);
+    pf[1] = pack_bf16(s_acc[0][2], s_acc[0][3]);
+    pf[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
+    pf[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; dt += 2) {
+      const int mi = lane >> 3;
+      const int key = warp * 16 + (mi & 1) * 8 + (lane & 7);
+      const int d = (dt + (mi >> 1)) * 8;
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4_trans(smem_u32(tV + key * ROW_ELEMS + d), r0, r1, r2, r3);
+      mma_bf16(o_acc[dt], pf, r0, r1);
+      mma_bf16(o_acc[dt + 1], pf, r2, r3);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();                                      // every warp is done with the stages: reuse them
+  if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
+
+  float* merge_o = reinterpret_cast<float*>(smem_raw);                  // [warps][16][HD]
+  float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                      // [warps][16][2]
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    const int r = g8 + 8 * i;
+    float* dst = merge_o + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d)
+      *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o_acc[d][2 * i], o_acc[d][2 * i + 1]);
+    if (t4 == 0) {
+      merge_ml[(warp * 16 + r) * 2] = m_run[i];
+      merge_ml[(warp * 16 + r) * 2 + 1] = l_run[i];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < p.group * HD; idx += DEC_WARPS * 32) {
+    const int r = idx / HD, d = idx - r * HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+    const float m_use = m == -INFINITY ? 0.0f : m;
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float scale = exp2f(merge_ml[(w * 16 + r) * 2] - m_use);
+      l += scale * merge_ml[(w * 16 + r) * 2 + 1];
+      acc += scale * merge_o[((size_t)w * 16 + r) * HD + d];
+    }
+    const int head = kvh * p.group + r;
+    if (p.num_splits == 1) {
+      p.out[(size_t)token * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    } else {
+      const size_t slot = ((size_t)split * p.total_tokens + token) * p.heads + head;
+      p.partial_o[slot * HD + d] = acc;
+      if (d == 0) {
+        p.partial_ml[slot * 2] = m;
+        p.partial_ml[slot * 2 + 1] = l;
+      }
+    }
+  }
+}
+
 // Merges the split states of one (token, head): out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s,
 // over the splits that hold keys visible to the row, in split order.
 __global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
@@ -400,6 +603,8 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   p.out = (__nv_bfloat16*)out; p.status = status;
   p.q_stride = q_stride; p.out_stride = out_stride;
   p.max_pages = max_pages; p.num_pages = num_pages; p.page_size = page_size;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.num_seqs = num_seqs; p.total_tokens = tokens;
   p.heads = heads; p.kv_heads = kv_heads; p.group = group;
   p.window = window;
@@ -412,6 +617,33 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   p.partial_o = scratch;
   p.partial_ml = scratch ? scratch + (size_t)num_splits * tokens * heads * HD : nullptr;
 
+  if (max_q_len <= 1 && tokens == num_seqs && group <= 16) {
+    // stages, then one page id per page of the longest key range a block can own
+    const int range = num_splits > 1 ? p.split_tokens : max_ctx_len;
+    const size_t smem = (size_t)DEC_STAGES * STAGE_ELEMS * sizeof(__nv_bfloat16) + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
+    TGE_REQUIRE(smem <= 227 * 1024, "attention_decode: %d keys per block need %zu bytes of shared memory; use smaller splits", range, smem);
+    static size_t configured = 0;
+    if (smem > configured) {
+      cudaError_t err = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) {
+        tge_set_error("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+        return -2;
+      }
+      configured = smem;
+    }
+    p.bq = 1;
+    dim3 grid(num_seqs, kv_heads, num_splits);
+    attention_decode_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(p);
+    int rc = tge_check_launch("attention_decode");
+    if (rc != 0) return rc;
+    if (num_splits > 1) {
+      dim3 mgrid(tokens, heads);
+      attention_merge_kernel<<<mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
+          p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+      return tge_launched("attention_merge", 2);
+    }
+    return 1;
+  }
   // rows per block: one warp (16 rows) per block when every portion is a single token and the group fits
   int nwarps = 4;
   if (max_q_len <= 1) nwarps = group <= 16 ? 1 : (group <= 32 ? 2 : 4);

@@ -283,6 +283,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tc_load16(taddr, r);
         const int m0 = tile_t * p.bn + c0;
         if (m0 >= p.m_tok) continue;                              // uniform over the warp
+        if (p.splits == 1 && p.epilogue == GEMM_ADD_F32) {
+          // read all sixteen old values before the first store, so the loads overlap
+          float* dst = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.ldo + n;
+          float old[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) old[j] = (n_ok && m0 + j < p.m_tok) ? dst[(size_t)j * p.ldo] : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + __uint_as_float(r[j]) + bias;
+          continue;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = m0 + j;
@@ -295,8 +306,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
               reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, other));
           } else if (n_ok && m < p.m_tok) {
             if (p.epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-            else if (p.epilogue == GEMM_STORE_F32) reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] += v;
+            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
           }
         }
       }
@@ -429,10 +439,19 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   const long long tiles = (long long)tiles_w * ((M + bn - 1) / bn);
   int splits = 1;
   if (force_splits > 0) splits = force_splits;
-  else if (tiles * 2 <= sms && k_blocks >= 8) {
-    splits = (int)((sms + tiles - 1) / tiles);
-    if (splits > k_blocks / 4) splits = k_blocks / 4;
-    if (splits > 16) splits = 16;
+  else if (tiles < sms && k_blocks >= 8) {
+    // Few tiles: cut k so that the work items fill whole waves of the persistent grid.  The cost of a
+    // choice is waves x (k-blocks per item + a fixed per-item overhead, in k-blocks); ties go to fewer splits.
+    const int overhead = 6;
+    long long best_cost = -1;
+    const int most = k_blocks / 4 < 32 ? k_blocks / 4 : 32;
+    for (int s = 1; s <= most; ++s) {
+      if ((long long)s * M * N > scratch_floats && s > 1) break;
+      const long long items = tiles * s;
+      const long long waves = (items + sms - 1) / sms;
+      const long long cost = waves * ((k_blocks + s - 1) / s + overhead);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = s; }
+    }
   }
   if (splits > k_blocks) splits = k_blocks;
   while (splits > 1 && (long long)splits * M * N > scratch_floats) --splits;

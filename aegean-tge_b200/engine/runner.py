@@ -28,7 +28,7 @@ class ModelRunner:
         """``use_graphs``: steps made only of single tokens replay a CUDA graph captured per batch size."""
         self.use_graphs = use_graphs and not cache.state_specs      # stateful toy mixers loop on the host
         self.max_graph_batch = max_graph_batch
-        self._graphs: Dict[int, "DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "DecodeGraph"] = {}
         self.graph_replays = 0
         self.model = model
         self.cache = cache
@@ -83,9 +83,13 @@ class ModelRunner:
         slots = [self.cache.slot_of(r) for r in requests]
         batch = len(portions)
         if self.use_graphs and batch <= self.max_graph_batch and all(len(p.tokens) == 1 for p in portions):
-            graph = self._graphs.get(batch)
+            bound = 1024
+            while bound < max(starts) + 1:
+                bound *= 2
+            bound = min(bound, self.max_model_len)
+            graph = self._graphs.get((batch, bound))
             if graph is None:
-                graph = self._graphs[batch] = DecodeGraph(self, batch)
+                graph = self._graphs[(batch, bound)] = DecodeGraph(self, batch, bound)
             tables = [self.cache.block_table(g, requests, width=graph.width) for g in range(len(self.cache.groups))]
             logits = graph.run([int(p.tokens[0]) for p in portions], starts, slots, tables)
             self.ops.launches += graph.kernels
@@ -116,17 +120,18 @@ class DecodeGraph:
     """One CUDA graph of a decode step for a fixed number of requests.
 
     All index arrays live in one static device buffer that is refilled from a
-    pinned host buffer before each replay; launch geometry is captured for the
-    longest context the engine allows, and blocks whose key range is empty
-    return at once, so one graph serves every context length.
+    pinned host buffer before each replay; launch geometry is captured for a
+    context bound (a power of two), and blocks whose key range is empty return
+    at once, so one graph serves every context length up to its bound.
     """
 
-    def __init__(self, runner: "ModelRunner", batch: int):
+    def __init__(self, runner: "ModelRunner", batch: int, max_ctx: int):
         from ..parts.base import StepContext
         self.batch = batch
+        self.max_ctx = max_ctx
         model, cache = runner.model, runner.cache
         device = runner.device
-        self.width = -(-runner.max_model_len // cache.page_size)
+        self.width = -(-max_ctx // cache.page_size)
         groups = len(cache.groups)
         sizes = [("token_ids", batch), ("positions", batch), ("seq_of_token", batch), ("q_start", batch + 1),
                  ("start_pos", batch), ("ctx_len", batch), ("slots", batch), ("rows", batch)]
@@ -160,7 +165,7 @@ class DecodeGraph:
             num_tokens=batch, num_seqs=batch, token_ids=d["token_ids"], positions=d["positions"],
             seq_of_token=d["seq_of_token"], q_start=d["q_start"], start_pos=d["start_pos"], ctx_len=d["ctx_len"],
             slots=d["slots"], block_tables=[d[f"table{g}"].view(batch, self.width) for g in range(groups)],
-            max_q_len=1, max_ctx_len=runner.max_model_len, host_q_lens=[1] * batch, host_start_pos=[0] * batch,
+            max_q_len=1, max_ctx_len=max_ctx, typical_ctx_len=max_ctx // 2 + 1, host_q_lens=[1] * batch, host_start_pos=[0] * batch,
             host_slots=[0] * batch)
         self.rows = d["rows"]
         ops = runner.ops

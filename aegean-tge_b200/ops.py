@@ -330,7 +330,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               q_start: torch.Tensor, start_pos: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
               num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int, kv_heads: int, head_dim: int,
               scale: float, window: int = 0, split_tokens: int = 0, out: Optional[torch.Tensor] = None,
-              force_simt: bool = False) -> torch.Tensor:
+              force_simt: bool = False, typical_ctx_len: int = 0) -> torch.Tensor:
     """Paged causal attention of a flat batch of portions.
 
     q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
@@ -360,7 +360,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     if use_mma:
         lib = attention_lib(head_dim)
         if split_tokens == 0:
-            split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, max_ctx_len, heads, kv_heads)
+            split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, typical_ctx_len or max_ctx_len,
+                                                  heads, kv_heads)
         splits = 1 if split_tokens == 0 or max_ctx_len <= split_tokens else -(-max_ctx_len // split_tokens)
         need = lib.tge_attention_mma_scratch_floats(tokens, heads, splits)
         scratch = scratch_floats(need) if need > 0 else None
@@ -389,10 +390,12 @@ def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_l
     if max_ctx_len <= 256:
         return 0
     group = heads // kv_heads
-    rows = 64 if max_q_len > 1 else (16 if group <= 16 else (32 if group <= 32 else 64))
-    bq = max(rows // group, 1)
-    tiles = -(-tokens // bq) if max_q_len > 1 else num_seqs
-    blocks = tiles * kv_heads
+    if max_q_len <= 1 and group <= 16:
+        blocks = num_seqs * kv_heads                      # the decode kernel: one block per (request, kv head)
+    else:
+        rows = 64 if max_q_len > 1 else (32 if group <= 32 else 64)
+        bq = max(rows // group, 1)
+        blocks = (-(-tokens // bq) if max_q_len > 1 else num_seqs) * kv_heads
     target = 2 * 148
     if blocks >= target:
         return 0

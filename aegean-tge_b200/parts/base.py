@@ -111,7 +111,8 @@ class StepContext:
     slots: torch.Tensor                # [S] per-request state slot
     block_tables: List[torch.Tensor]   # per page group: [S, max_pages] physical page ids
     max_q_len: int                     # host copies, for launch geometry
-    max_ctx_len: int
+    max_ctx_len: int                   # an upper bound (launch geometry); contexts may be shorter
+    typical_ctx_len: int = 0           # what contexts are expected to be (0: the bound); tunes splitting only
     host_q_lens: List[int] = field(default_factory=list)
     host_start_pos: List[int] = field(default_factory=list)
     host_slots: List[int] = field(default_factory=list)
