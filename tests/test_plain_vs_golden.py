@@ -1,0 +1,38 @@
+"""The plain implementation against the reference's own model code (no GPU).
+
+tests/golden/tiny_<name>.npz hold logits that the reference's Qwen2 class produced on the CPU
+(scalar attention and kernels, float32) for the tiny random models A and B: after a whole prompt,
+after single decode steps, for every row of a batch, and for a mixed batch of two sequences
+(tests/golden/make_golden.py made them).  The plain float64 implementation must agree with them to
+float32 rounding.  The weights are regenerated from the seed; if the generator behind them ever
+changes, their hash no longer matches and the comparison is skipped rather than misreported.
+"""
+import hashlib
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, TINY
+from plain import qwen2_plain as plain
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_plain_matches_the_reference_model(model_dirs, name):
+    golden = np.load(os.path.join(ROOT, "tests", "golden", f"tiny_{name}.npz"))
+    config, weights = plain.read_model(model_dirs[name])
+    digest = hashlib.sha256()
+    for key in sorted(weights):
+        digest.update(key.encode())
+        digest.update(weights[key].float().numpy().astype("<f4").tobytes())
+    if digest.hexdigest() != str(golden["weights_sha256"]):
+        pytest.skip("the seeded weights differ from those the golden files were made with")
+    sequences = {0: [int(t) for t in golden["first"]], 1: [int(t) for t in golden["second"]]}
+    full = {s: plain.logits_of(config, weights, tokens).float().numpy() for s, tokens in sequences.items()}
+    expected = np.stack([full[int(s)][int(p)] for s, p in zip(golden["row_sequence"], golden["row_position"])])
+    got = golden["logits"]
+    scale = float(np.abs(got).max())
+    worst = float(np.abs(expected - got).max())
+    assert worst < 2e-6 * max(scale, 1.0), (worst, scale)
+    assert (expected.argmax(-1) == got.argmax(-1)).all()
