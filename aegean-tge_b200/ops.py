@@ -73,6 +73,11 @@ def core() -> ctypes.CDLL:
                                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
                                              _c_int, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_sample", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_apply_penalty", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_sample_cuts", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                          _c_int, _c_int, _c_ptr])
+        lib.tge_sample_cuts_padded.argtypes = [_c_int]
+        lib.tge_sample_cuts_padded.restype = _c_ll
         _core_lib = lib
     return _core_lib
 
@@ -422,4 +427,47 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tenso
     lib = core()
     _check(lib.tge_sample(logits.data_ptr(), stride, temperature.data_ptr(), uniform.data_ptr(), out.data_ptr(), rows,
                           vocab, _stream()), lib)
+    return out
+
+
+def apply_penalty(logits: torch.Tensor, history: torch.Tensor, history_start: torch.Tensor,
+                  penalty: torch.Tensor) -> torch.Tensor:
+    """A copy of ``logits`` (float32 [R, V]) with the repetition penalty applied.
+
+    ``history`` (int32) is every row's window of recent tokens, one after another;
+    ``history_start`` (int32 [R + 1]) its offsets; ``penalty`` float32 [R], 1.0 = off.
+    """
+    _want(logits, "logits", torch.float32, contiguous=False)
+    stride = _rows_2d(logits, "logits")
+    rows, vocab = logits.shape
+    for name, t, dtype in (("history", history, torch.int32), ("history offsets", history_start, torch.int32),
+                           ("penalty", penalty, torch.float32)):
+        _want(t, name, dtype)
+    out = logits.clone()
+    lib = core()
+    _check(lib.tge_apply_penalty(logits.data_ptr(), out.data_ptr(), stride, history.data_ptr(),
+                                 history_start.data_ptr(), penalty.data_ptr(), rows, vocab, _stream()), lib)
+    return out
+
+
+def sample_cuts(scores: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                min_p: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
+    """One token per row with the top-k / min-p / top-p cuts (0 / 0.0 / 1.0 switch a cut off)."""
+    _want(scores, "scores", torch.float32, contiguous=False)
+    stride = _rows_2d(scores, "scores")
+    rows, vocab = scores.shape
+    for name, t, dtype in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                           ("top_p", top_p, torch.float32), ("min_p", min_p, torch.float32),
+                           ("uniform draws", uniform, torch.float32)):
+        _want(t, name, dtype)
+        if t.numel() != rows:
+            raise KernelError(f"sample_cuts: one {name} per row")
+    lib = core()
+    padded = lib.tge_sample_cuts_padded(vocab)
+    sort_prob = torch.empty((rows, padded), dtype=torch.float32, device=scores.device)
+    sort_index = torch.empty((rows, padded), dtype=torch.int32, device=scores.device)
+    out = torch.empty(rows, dtype=torch.int32, device=scores.device)
+    _check(lib.tge_sample_cuts(scores.data_ptr(), stride, temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
+                               min_p.data_ptr(), uniform.data_ptr(), sort_prob.data_ptr(), sort_index.data_ptr(),
+                               out.data_ptr(), rows, vocab, _stream()), lib)
     return out

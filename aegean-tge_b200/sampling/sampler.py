@@ -1,11 +1,14 @@
 """Turns logits rows into token ids on the device.
 
-Greedy and temperature sampling follow src/models/sampling.cpp:183-228:
-the first maximal index when the temperature is not positive; otherwise
-``exp((z - max) / T)`` summed in index order, a uniform draw scaled by the
-sum, and the first index at which the running remainder drops to zero or
-below.  Each request owns its xorshift32 state on the host; one draw is
-consumed per sampled token and passed to the kernel.
+Follows src/models/sampling.cpp:183-410: scores are the logits with the
+repetition penalty applied (each distinct token of the recent history window
+once); a non-positive temperature takes the first maximal index; otherwise
+``exp((z - max) / T)``, the top-k / min-p / top-p cuts over candidates ordered
+by probability, a uniform draw scaled by the kept mass, and the first
+candidate at which the running remainder drops to zero or below.  Each request
+owns its xorshift32 state on the host; one draw is consumed per sampled token
+(none for greedy rows) and passed to the kernel.  Rows without cuts take the
+kernel that needs no sort.
 """
 from __future__ import annotations
 
@@ -21,22 +24,51 @@ class Sampler:
         self.ops = ops
         self.device = device
 
+    def _to_device(self, values, dtype) -> torch.Tensor:
+        host = torch.tensor(values, dtype=dtype)
+        if self.device.type == "cuda":
+            host = host.pin_memory()
+        return host.to(self.device, non_blocking=True)
+
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[XorShift32],
                histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
-        """One token id per row of ``logits`` (float32 [R, vocab])."""
+        """One token id per row of ``logits`` (float32 [R, vocab]).
+
+        ``histories`` (prompt plus generated tokens of each row's request) feeds only the penalty.
+        """
         rows = logits.shape[0]
         if rows != len(params) or rows != len(rngs):
             raise ValueError("sampler: one SamplingParams and one generator per logits row")
         temperatures, uniforms = [], []
         for p, rng in zip(params, rngs):
             p.validate()
-            if p.has_cuts or p.has_penalty:
-                raise NotImplementedError("sampler: top-k / top-p / min-p / repeat penalty are not built yet")
             temperatures.append(max(float(p.temperature), 0.0))
             uniforms.append(0.0 if p.greedy else rng.next_uniform())
-        host = torch.tensor([temperatures, uniforms], dtype=torch.float32)
-        if self.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        ids = self.ops.sample(logits, dev[0], dev[1])
+        scores = logits
+        if any(p.has_penalty for p in params):
+            if histories is None:
+                raise ValueError("sampler: a repetition penalty needs the token histories")
+            flat: List[int] = []
+            starts = [0]
+            for p, history in zip(params, histories):
+                if p.has_penalty:
+                    window = history[-p.penalty_window:] if p.penalty_window > 0 else history
+                    flat.extend(int(t) for t in window)
+                starts.append(len(flat))
+            scores = self.ops.apply_penalty(logits, self._to_device(flat or [0], torch.int32),
+                                            self._to_device(starts, torch.int32),
+                                            self._to_device([float(p.repeat_penalty) for p in params], torch.float32))
+        floats = self._to_device([temperatures, uniforms], torch.float32)
+        cut_rows = [i for i, p in enumerate(params) if p.has_cuts and not p.greedy]
+        if not cut_rows:
+            return self.ops.sample(scores, floats[0], floats[1]).cpu().tolist()
+        ids = self.ops.sample(scores, floats[0], floats[1])
+        picked = self._to_device(cut_rows, torch.int64)
+        cut_ids = self.ops.sample_cuts(
+            scores.index_select(0, picked), floats[0].index_select(0, picked),
+            self._to_device([params[i].top_k for i in cut_rows], torch.int32),
+            self._to_device([params[i].top_p for i in cut_rows], torch.float32),
+            self._to_device([params[i].min_p for i in cut_rows], torch.float32),
+            floats[1].index_select(0, picked))
+        ids[picked] = cut_ids
         return ids.cpu().tolist()

@@ -198,3 +198,56 @@ def sample_plain(logits: np.ndarray, temperature: float, rng: PlainXorShift32) -
         if target <= 0:
             return i
     return len(e) - 1
+
+
+def penalize_plain(logits: np.ndarray, history: Sequence[int], penalty: float, window: int) -> np.ndarray:
+    """Repetition penalty (src/models/sampling.cpp:32-54): each distinct token of the last ``window``
+    history tokens (0 = all) once; positive scores are divided, negative ones multiplied."""
+    scores = logits.astype(np.float32).copy()
+    if not (penalty > 0.0 and penalty != 1.0 and len(history) > 0):
+        return scores
+    begin = max(0, len(history) - window) if window > 0 else 0
+    seen = set()
+    for token in reversed(history[begin:]):
+        if token < 0 or token >= len(scores) or token in seen:
+            continue
+        seen.add(token)
+        scores[token] = scores[token] / np.float32(penalty) if scores[token] > 0 else scores[token] * np.float32(penalty)
+    return scores
+
+
+def sample_cuts_plain(scores: np.ndarray, temperature: float, top_k: int, top_p: float, min_p: float, u: float) -> int:
+    """Temperature draw with the top-k / min-p / top-p cuts (src/models/sampling.cpp:230-410), float32,
+    sequential.  Candidates are ordered by probability, highest first, lower index first among equals."""
+    scores = scores.astype(np.float32)
+    count = len(scores)
+    inv = np.float32(1.0) / np.float32(temperature)
+    prob = np.exp((scores - scores.max()) * inv).astype(np.float32)
+    order = sorted(range(count), key=lambda i: (-float(prob[i]), i))
+    keep = min(top_k, count) if top_k > 0 else count
+    order = order[:keep]
+    if min_p > 0.0:
+        floor = np.float32(min_p) * prob[order[0]]
+        order = [i for i in order if prob[i] >= floor]
+    total = np.float32(0.0)
+    for i in order:
+        total = np.float32(total + prob[i])
+    if not order or not total > 0:
+        return int(np.argmax(prob))
+    limit = len(order)
+    if top_p < 1.0:
+        cumulative = np.float32(0.0)
+        for n, i in enumerate(order):
+            cumulative = np.float32(cumulative + prob[i])
+            if cumulative / total >= np.float32(top_p):
+                limit = n + 1
+                break
+    kept = np.float32(0.0)
+    for i in order[:limit]:
+        kept = np.float32(kept + prob[i])
+    target = np.float32(np.float32(u) * kept)
+    for i in order[:limit]:
+        target = np.float32(target - prob[i])
+        if target <= 0:
+            return i
+    return order[limit - 1]
