@@ -16,6 +16,11 @@
 //
 // Masking is by absolute position: key t is visible to the query at position p
 // when t <= p and, with a window w > 0, t > p - w.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
 #include "common.cuh"
 
 #ifndef TGE_HEAD_DIM
@@ -516,6 +521,320 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
   }
 }
 
+// ---------------------------------------------------------------------------
+// Decode for head sizes that are multiples of 64: the same block and warp layout as above, but the
+// tiles come by TMA.  The page pool of a layer is one 2-D tensor [pages * kv_heads * page_size,
+// head_dim]; one box is one page of one kv head by 64 columns (128 bytes, 128-byte swizzle), so a
+// tile of 64 positions is 64 / page_size boxes per 64-column block for K and as many for V, issued by
+// one thread and counted by an mbarrier per stage.  ldmatrix addresses apply the same swizzle.
+// Stages are cleared once at the start: boxes of pages a request does not own are never fetched,
+// and what masked columns multiply must be finite.
+// ---------------------------------------------------------------------------
+#if TGE_HEAD_DIM % 64 == 0
+constexpr int TMA_BLOCKS = HD / 64;                       // 64-column blocks per row
+constexpr int TMA_TILE_BYTES = BKV * HD * 2;              // one K (or V) tile
+constexpr int TMA_STAGE_BYTES = 2 * TMA_TILE_BYTES;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about two seconds, records it, and lets the caller go on.
+__device__ __forceinline__ void mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
+  if (mbar_try_wait(bar, parity)) return;
+  unsigned long long start;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(start));
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((spin & 1023u) == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(now));
+      if (now - start > 2000000000ull) {
+        if (status) atomicOr(status, TGE_STATUS_WAIT_TIMEOUT);
+        return;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// byte offset of the 16-byte chunk holding columns [col, col + 8) of row `row` inside a swizzled tile
+__device__ __forceinline__ uint32_t swizzled(int row, int col) {
+  const int block = col >> 6, chunk = (col & 63) >> 3;
+  return (uint32_t)(block * (BKV * 128) + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzle atoms are 1024 bytes
+  unsigned char* generic = smem_dyn + (base - raw);
+  const uint32_t bars = base + DEC_STAGES * TMA_STAGE_BYTES;          // one mbarrier per stage
+  int* local_table = reinterpret_cast<int*>(generic + DEC_STAGES * TMA_STAGE_BYTES + 64);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int token = p.q_start[seq];
+  const int pos = p.start_pos[seq];
+  int lo = p.window > 0 ? max(pos - p.window + 1, 0) : 0;
+  int hi = pos + 1;
+  if (p.num_splits > 1) {
+    lo = max(lo, split * p.split_tokens);
+    hi = min(hi, (split + 1) * p.split_tokens);
+  }
+  if (lo >= hi) return;
+
+  const int k_first = lo / BKV * BKV;
+  const int num_tiles = (hi - k_first + BKV - 1) / BKV;
+  const int first_page = k_first >> p.page_shift;
+  const int last_page = (k_first + num_tiles * BKV - 1) >> p.page_shift;
+  for (int i = first_page + tid; i <= last_page; i += DEC_WARPS * 32) {
+    int page = i < p.max_pages ? p.block_table[(size_t)seq * p.max_pages + i] : -1;
+    if (page >= p.num_pages) page = -2;                                // reported below, never fetched
+    local_table[i - first_page] = page;
+  }
+  {
+    uint4* fill = reinterpret_cast<uint4*>(generic);
+    for (int i = tid; i < DEC_STAGES * TMA_STAGE_BYTES / 16; i += DEC_WARPS * 32) fill[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // the cleared stages, before TMA writes them
+  __syncthreads();
+
+  const int pages_per_tile = BKV >> p.page_shift;
+  auto issue = [&](int tile) {                                          // thread 0 only
+    const int stage = tile % DEC_STAGES;
+    const uint32_t k_dst = base + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
+    const uint32_t bar = bars + 8 * stage;
+    int boxes = 0;
+    for (int j = 0; j < pages_per_tile; ++j) {
+      const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
+      if (page >= 0 && (k_first + tile * BKV + (j << p.page_shift)) < hi) ++boxes;
+    }
+    mbar_expect_tx(bar, (uint32_t)boxes * 2u * TMA_BLOCKS * (uint32_t)(p.page_size * 128));
+    for (int j = 0; j < pages_per_tile; ++j) {
+      const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
+      if (page < 0 || (k_first + tile * BKV + (j << p.page_shift)) >= hi) continue;
+      const int row = (page * p.kv_heads + kvh) << p.page_shift;
+#pragma unroll
+      for (int b = 0; b < TMA_BLOCKS; ++b) {
+        const uint32_t offset = (uint32_t)(b * (BKV * 128) + (j << p.page_shift) * 128);
+        tma_load_2d(k_dst + offset, &map_k, bar, b * 64, row);
+        tma_load_2d(v_dst + offset, &map_v, bar, b * 64, row);
+      }
+    }
+  };
+  if (tid == 0) {
+    for (int s = 0; s < DEC_STAGES - 1 && s < num_tiles; ++s) issue(s);
+  }
+
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = g8 + 8 * i;
+      const bool valid = r < p.group;
+      const __nv_bfloat16* src = p.q + (size_t)token * p.q_stride + (size_t)(kvh * p.group + (valid ? r : 0)) * HD + kc * 16 + 2 * t4;
+      qf[kc][i] = valid ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+      qf[kc][i + 2] = valid ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+    }
+  }
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[d][e] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  bool bad_page = false;
+
+  for (int it = 0; it < num_tiles; ++it) {
+    __syncthreads();                                     // everyone is done with the stage tile it-1 used
+    if (tid == 0 && it + DEC_STAGES - 1 < num_tiles) issue(it + DEC_STAGES - 1);
+    const int stage = it % DEC_STAGES;
+    mbar_wait_bounded(bars + 8 * stage, (uint32_t)(it / DEC_STAGES) & 1u, p.status);
+    const uint32_t tK = base + stage * TMA_STAGE_BYTES, tV = tK + TMA_TILE_BYTES;
+    const int k0 = k_first + it * BKV + warp * 16;
+    if (k0 >= hi || k0 + 16 <= lo) continue;
+    if (local_table[(max(k0, lo) >> p.page_shift) - first_page] < 0) bad_page = true;   // a visible position without a page
+
+    float s_acc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_acc[n][e] = 0.0f;
+#pragma unroll
+    for (int kc = 0; kc < HD / 16; ++kc) {
+      const int mi = lane >> 3;
+      const int n = warp * 16 + (mi >> 1) * 8 + (lane & 7);
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4(tK + swizzled(n, kc * 16 + (mi & 1) * 8), r0, r1, r2, r3);
+      mma_bf16(s_acc[0], qf[kc], r0, r1);
+      mma_bf16(s_acc[1], qf[kc], r2, r3);
+    }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const bool row_valid = g8 + 8 * i < p.group;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kpos = k0 + n * 8 + 2 * t4 + e;
+          const bool visible = row_valid && kpos >= lo && kpos < hi;
+          const float sv = visible ? s_acc[n][2 * i + e] * p.scale_log2 : -INFINITY;
+          s_acc[n][2 * i + e] = sv;
+          mx = fmaxf(mx, sv);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[i], mx);
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+      corr[i] = exp2f(m_run[i] - m_use);
+      float sum = 0.0f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float pv = exp2f(s_acc[n][2 * i + e] - m_use);
+          s_acc[n][2 * i + e] = pv;
+          sum += pv;
+        }
+      }
+      l_run[i] = l_run[i] * corr[i] + sum;
+      m_run[i] = m_new;
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {   // the maximum moved: rescale
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d) {
+        o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
+        o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
+      }
+    }
+    uint32_t pf[4];
+    pf[0] = pack_bf16(s_acc[0][0], s_acc[0][1]);
+    pf[1] = pack_bf16(s_acc[0][2], s_acc[0][3]);
+    pf[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
+    pf[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; dt += 2) {
+      const int mi = lane >> 3;
+      const int key = warp * 16 + (mi & 1) * 8 + (lane & 7);
+      uint32_t r0, r1, r2, r3;
+      ldmatrix_x4_trans(tV + swizzled(key, (dt + (mi >> 1)) * 8), r0, r1, r2, r3);
+      mma_bf16(o_acc[dt], pf, r0, r1);
+      mma_bf16(o_acc[dt + 1], pf, r2, r3);
+    }
+  }
+  __syncthreads();                                       // all tiles consumed, no copy in flight: reuse the stages
+  if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
+
+  float* merge_o = reinterpret_cast<float*>(generic);                   // [warps][16][HD]
+  float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                      // [warps][16][2]
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    const int r = g8 + 8 * i;
+    float* dst = merge_o + ((size_t)warp * 16 + r) * HD;
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d)
+      *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o_acc[d][2 * i], o_acc[d][2 * i + 1]);
+    if (t4 == 0) {
+      merge_ml[(warp * 16 + r) * 2] = m_run[i];
+      merge_ml[(warp * 16 + r) * 2 + 1] = l_run[i];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < p.group * HD; idx += DEC_WARPS * 32) {
+    const int r = idx / HD, d = idx - r * HD;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+    const float m_use = m == -INFINITY ? 0.0f : m;
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float scale = exp2f(merge_ml[(w * 16 + r) * 2] - m_use);
+      l += scale * merge_ml[(w * 16 + r) * 2 + 1];
+      acc += scale * merge_o[((size_t)w * 16 + r) * HD + d];
+    }
+    const int head = kvh * p.group + r;
+    if (p.num_splits == 1) {
+      p.out[(size_t)token * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+    } else {
+      const size_t slot = ((size_t)split * p.total_tokens + token) * p.heads + head;
+      p.partial_o[slot * HD + d] = acc;
+      if (d == 0) {
+        p.partial_ml[slot * 2] = m;
+        p.partial_ml[slot * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The tensor map of a page pool, made once per (address, geometry) and kept.
+const CUtensorMap* pool_map(const void* pages, int num_pages, int kv_heads, int page_size) {
+  static EncodeTiledFn encode = nullptr;
+  static bool tried = false;
+  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> maps;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  if (!encode) {
+    tge_set_error("attention_decode: the driver does not export cuTensorMapEncodeTiled");
+    return nullptr;
+  }
+  const auto key = std::make_tuple(pages, num_pages, kv_heads, page_size);
+  auto found = maps.find(key);
+  if (found != maps.end()) return &found->second;
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)num_pages * kv_heads * page_size};
+  cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult rc = encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, elem,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    tge_set_error("attention_decode: cuTensorMapEncodeTiled failed with code %d", (int)rc);
+    return nullptr;
+  }
+  return &maps.emplace(key, map).first->second;
+}
+#endif  // TGE_HEAD_DIM % 64 == 0
+
 // Merges the split states of one (token, head): out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s,
 // over the splits that hold keys visible to the row, in split order.
 __global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
@@ -617,6 +936,37 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   p.partial_o = scratch;
   p.partial_ml = scratch ? scratch + (size_t)num_splits * tokens * heads * HD : nullptr;
 
+#if TGE_HEAD_DIM % 64 == 0
+  if (max_q_len <= 1 && tokens == num_seqs && group <= 16 && page_size >= 8) {
+    const CUtensorMap* map_k = pool_map(k_pages, num_pages, kv_heads, page_size);
+    const CUtensorMap* map_v = pool_map(v_pages, num_pages, kv_heads, page_size);
+    if (!map_k || !map_v) return -3;
+    const int range = (num_splits > 1 ? p.split_tokens : max_ctx_len) + 2 * BKV;
+    const size_t smem = 1024 + (size_t)DEC_STAGES * TMA_STAGE_BYTES + 64 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
+    TGE_REQUIRE(smem <= 227 * 1024, "attention_decode: %d keys per block need %zu bytes of shared memory; use smaller splits", range, smem);
+    static size_t configured = 0;
+    if (smem > configured) {
+      cudaError_t err = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) {
+        tge_set_error("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+        return -2;
+      }
+      configured = smem;
+    }
+    p.bq = 1;
+    dim3 grid(num_seqs, kv_heads, num_splits);
+    attention_decode_tma_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(*map_k, *map_v, p);
+    int rc = tge_check_launch("attention_decode_tma");
+    if (rc != 0) return rc;
+    if (num_splits > 1) {
+      dim3 mgrid(tokens, heads);
+      attention_merge_kernel<<<mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
+          p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+      return tge_launched("attention_merge", 2);
+    }
+    return 1;
+  }
+#endif
   if (max_q_len <= 1 && tokens == num_seqs && group <= 16) {
     // stages, then one page id per page of the longest key range a block can own
     const int range = num_splits > 1 ? p.split_tokens : max_ctx_len;
