@@ -47,6 +47,7 @@ struct GemmParams {
   int k_blocks, tiles_w, tiles_t;
   int epilogue;
   int acc_cols;        // tensor-memory columns allocated (power of two >= 32)
+  int to_partial;      // write float32 partial sums to `partial` instead of applying the epilogue
   const float* bias;
   void* out;
   long long ldo;
@@ -276,14 +277,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       tc_fence_after();
       const int n = tile_w * BM + quarter * 32 + lane;          // weight row = output feature
       const bool n_ok = n < p.n_w;
-      const float bias = (p.bias && n_ok && p.splits == 1) ? p.bias[n] : 0.0f;
+      const float bias = (p.bias && n_ok && !p.to_partial) ? p.bias[n] : 0.0f;
       for (int c0 = 0; c0 < p.bn; c0 += 16) {
         uint32_t r[16];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.bn + c0);
         tc_load16(taddr, r);
         const int m0 = tile_t * p.bn + c0;
         if (m0 >= p.m_tok) continue;                              // uniform over the warp
-        if (p.splits == 1 && p.epilogue == GEMM_ADD_F32) {
+        if (!p.to_partial && p.epilogue == GEMM_ADD_F32) {
           // read all sixteen old values before the first store, so the loads overlap
           float* dst = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.ldo + n;
           float old[16];
@@ -298,7 +299,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int j = 0; j < 16; ++j) {
           const int m = m0 + j;
           float v = __uint_as_float(r[j]) + bias;
-          if (p.splits > 1) {
+          if (p.to_partial) {
             if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
           } else if (p.epilogue == GEMM_SWIGLU) {
             const float other = __shfl_xor_sync(0xffffffffu, v, 1);
@@ -468,25 +469,20 @@ TGE_API long long tge_gemm_tcgen05_scratch_floats(int M, int N, int K) {
   return plan.splits > 1 ? (long long)plan.splits * M * N : 0;
 }
 
-// x [M, K] bf16 (row stride ldx), w [N, K] bf16 (row stride ldw); bias float32 [N] or null;
-// out per epilogue (row stride ldo elements).  scratch: float32 buffer of scratch_floats
-// elements for split-k partial sums (may be null: no split).  force_bn / force_splits: 0 = automatic.
-// Returns TGE_UNSUPPORTED (and touches nothing) when the shape cannot go through TMA: K not a
-// multiple of 8, misaligned pointers or strides.  The caller then uses the CUDA-core product.
-TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
-                             long long ldo, int M, int N, int K, int epilogue, float* scratch,
-                             long long scratch_floats, int force_bn, int force_splits, int* status,
-                             cudaStream_t stream) {
-  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_SWIGLU, "gemm: unknown epilogue %d", epilogue);
-  TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
-  TGE_REQUIRE(force_bn == 0 || (force_bn % 16 == 0 && force_bn >= 16 && force_bn <= 256), "gemm: token tile %d must be a multiple of 16 in [16, 256]", force_bn);
-  TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
-  if (M == 0) return 0;
+namespace {
+
+// Launches the product kernel.  With `partial_always` (or when the plan cuts k) the kernel leaves
+// float32 partial sums [splits, M, N] in `scratch` and *splits_out tells how many; the caller then
+// runs the kernel that adds them up.  Returns 1 (one kernel launched), TGE_UNSUPPORTED, or an error.
+int launch_product(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                   long long ldo, int M, int N, int K, int epilogue, float* scratch, long long scratch_floats,
+                   int force_bn, int force_splits, bool partial_always, int* status, cudaStream_t stream,
+                   int* splits_out) {
   if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)w % 16 != 0) return TGE_UNSUPPORTED;
   if (scratch == nullptr) scratch_floats = 0;
   const Plan plan = make_plan(M, N, K, scratch_floats, force_bn, force_splits);
-  TGE_REQUIRE(plan.splits == 1 || (long long)plan.splits * M * N <= scratch_floats,
+  const bool to_partial = partial_always || plan.splits > 1;
+  TGE_REQUIRE(!to_partial || (long long)plan.splits * M * N <= scratch_floats,
               "gemm_tcgen05: %d k-splits need %lld floats of scratch, have %lld", plan.splits,
               (long long)plan.splits * M * N, scratch_floats);
 
@@ -506,6 +502,7 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
   int cols = 32;
   while (cols < 2 * plan.bn) cols *= 2;
   p.acc_cols = cols;
+  p.to_partial = to_partial ? 1 : 0;
   p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
 
   const size_t smem = 1024 + (size_t)plan.stages * (A_STAGE_BYTES + plan.bn * BK * 2) + 8 * (2 * plan.stages + 4) + 16;
@@ -523,12 +520,183 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
   gemm_tcgen05_kernel<<<grid, NUM_THREADS, smem, stream>>>(map_w, map_x, p);
   rc = tge_check_launch("gemm_tcgen05");
   if (rc != 0) return rc;
-  if (plan.splits > 1) {
+  *splits_out = to_partial ? plan.splits : 0;
+  return 1;
+}
+
+// One block per token: stream[t, :] += sum of the k-split partial sums (+ bias), then RMSNorm of the
+// new row (same summation pattern as the stand-alone norm kernel) into norm_out.
+__global__ void splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
+                                       float* __restrict__ stream, long long ld_stream,
+                                       const float* __restrict__ norm_weight, float eps,
+                                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w,
+                                       int splits) {
+  extern __shared__ float row_values[];
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const size_t plane = (size_t)m_tok * n_w;
+  float sum = 0.0f;
+  for (int n = threadIdx.x; n < n_w; n += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) acc += partial[s * plane + (size_t)t * n_w + n];
+    if (bias) acc += bias[n];
+    const float v = stream[(size_t)t * ld_stream + n] + acc;
+    stream[(size_t)t * ld_stream + n] = v;
+    row_values[n] = v;
+    sum = fmaf(v, v, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = 1.0f / sqrtf(sum / (float)n_w + eps);
+  for (int n = threadIdx.x; n < n_w; n += blockDim.x)
+    norm_out[(size_t)t * ld_norm + n] = __float2bfloat16_rn(row_values[n] * scale * norm_weight[n]);
+}
+
+// One block per token: q, k, v = sum of the partial sums + bias; q rotated into the qkv buffer, k rotated
+// and v copied into their pages (formulas as in the stand-alone rotate-and-store kernel).
+__global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
+                                             __nv_bfloat16* __restrict__ qkv, long long ld_qkv, int m_tok, int n_w,
+                                             int splits, const float* __restrict__ cos_table,
+                                             const float* __restrict__ sin_table, int table_rows, int rotary,
+                                             const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                             const int* __restrict__ block_table, int max_pages,
+                                             __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                                             int num_pages, int page_size, int heads, int kv_heads, int head_dim,
+                                             int* status) {
+  extern __shared__ float row_values[];
+  const int t = blockIdx.x;
+  const size_t plane = (size_t)m_tok * n_w;
+  for (int n = threadIdx.x; n < n_w; n += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) acc += partial[s * plane + (size_t)t * n_w + n];
+    if (bias) acc += bias[n];
+    row_values[n] = acc;
+  }
+  __syncthreads();
+  const int pos = positions[t];
+  const int half = rotary / 2;
+  if (half > 0 && (pos < 0 || pos >= table_rows)) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+    return;
+  }
+  const float* cs = cos_table + (size_t)pos * half;
+  const float* sn = sin_table + (size_t)pos * half;
+  auto rotated = [&](const float* head, int d) -> float {
+    if (d < half) return head[d] * cs[d] - head[d + half] * sn[d];
+    if (d < rotary) return head[d - half] * sn[d - half] + head[d] * cs[d - half];
+    return head[d];
+  };
+  __nv_bfloat16* q_out = qkv + (size_t)t * ld_qkv;
+  for (int i = threadIdx.x; i < heads * head_dim; i += blockDim.x) {
+    const int h = i / head_dim, d = i - h * head_dim;
+    q_out[i] = __float2bfloat16_rn(rotated(row_values + (size_t)h * head_dim, d));
+  }
+  const int seq = seq_of_token[t];
+  const int page_index = pos / page_size;
+  const int page = page_index < max_pages ? block_table[(size_t)seq * max_pages + page_index] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+    return;
+  }
+  const int slot = pos - page_index * page_size;
+  const float* k_row = row_values + (size_t)heads * head_dim;
+  const float* v_row = k_row + (size_t)kv_heads * head_dim;
+  for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
+    const int h = i / head_dim, d = i - h * head_dim;
+    const size_t dst = (((size_t)page * kv_heads + h) * page_size + slot) * head_dim + d;
+    k_pages[dst] = __float2bfloat16_rn(rotated(k_row + (size_t)h * head_dim, d));
+    v_pages[dst] = __float2bfloat16_rn(v_row[i]);
+  }
+}
+
+constexpr int FUSED_MAX_TOKENS = 256;   // above this the product's own epilogue is the better path
+
+}  // namespace
+
+// x [M, K] bf16 (row stride ldx), w [N, K] bf16 (row stride ldw); bias float32 [N] or null;
+// out per epilogue (row stride ldo elements).  scratch: float32 buffer of scratch_floats
+// elements for split-k partial sums (may be null: no split).  force_bn / force_splits: 0 = automatic.
+// Returns TGE_UNSUPPORTED (and touches nothing) when the shape cannot go through TMA: K not a
+// multiple of 8, misaligned pointers or strides.  The caller then uses the CUDA-core product.
+TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                             long long ldo, int M, int N, int K, int epilogue, float* scratch,
+                             long long scratch_floats, int force_bn, int force_splits, int* status,
+                             cudaStream_t stream) {
+  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
+  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_SWIGLU, "gemm: unknown epilogue %d", epilogue);
+  TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
+  TGE_REQUIRE(force_bn == 0 || (force_bn % 16 == 0 && force_bn >= 16 && force_bn <= 256), "gemm: token tile %d must be a multiple of 16 in [16, 256]", force_bn);
+  TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
+  if (M == 0) return 0;
+  int splits = 0;
+  int rc = launch_product(x, ldx, w, ldw, bias, out, ldo, M, N, K, epilogue, scratch, scratch_floats, force_bn,
+                          force_splits, false, status, stream, &splits);
+  if (rc != 1) return rc;
+  if (splits > 0) {
     const long long count = epilogue == GEMM_SWIGLU ? (long long)M * N / 2 : (long long)M * N;
     long long blocks = (count + 255) / 256;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
-    splitk_epilogue_kernel<<<(int)blocks, 256, 0, stream>>>(scratch, bias, out, ldo, M, N, plan.splits, epilogue);
+    splitk_epilogue_kernel<<<(int)blocks, 256, 0, stream>>>(scratch, bias, out, ldo, M, N, splits, epilogue);
     return tge_launched("splitk_epilogue", 2);
   }
   return 1;
+}
+
+// stream [M, N] float32 += x . w^T (+ bias), then norm_out [M, N] bf16 = RMSNorm(stream rows) * norm_weight:
+// the product leaves partial sums in scratch and one kernel per token row adds them into the stream and
+// normalises the new row.  scratch must hold at least max(1, k-splits) * M * N floats.  Returns
+// TGE_UNSUPPORTED for more than 256 tokens or shapes TMA cannot address (use the separate kernels then).
+TGE_API int tge_gemm_tcgen05_add_norm(const void* x, long long ldx, const void* w, long long ldw, const float* bias,
+                                      float* stream_out, long long ldo, int M, int N, int K, const float* norm_weight,
+                                      float eps, void* norm_out, long long ld_norm, float* scratch,
+                                      long long scratch_floats, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+norm: bad sizes M=%d N=%d K=%d", M, N, K);
+  TGE_REQUIRE(status != nullptr && norm_weight != nullptr && norm_out != nullptr && eps > 0.0f, "gemm+norm: bad arguments");
+  if (M == 0) return 0;
+  if (M > FUSED_MAX_TOKENS || (size_t)N * sizeof(float) > 200 * 1024 || scratch == nullptr) return TGE_UNSUPPORTED;
+  int splits = 0;
+  int rc = launch_product(x, ldx, w, ldw, nullptr, stream_out, ldo, M, N, K, GEMM_ADD_F32, scratch, scratch_floats, 0, 0,
+                          true, status, stream, &splits);
+  if (rc != 1) return rc;
+  const size_t smem = (size_t)N * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaFuncSetAttribute(splitk_add_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = smem;
+  }
+  splitk_add_norm_kernel<<<M, N >= 2048 ? 512 : 256, smem, stream>>>(scratch, bias, stream_out, ldo, norm_weight, eps,
+                                                                   (__nv_bfloat16*)norm_out, ld_norm, M, N, splits);
+  return tge_launched("splitk_add_norm", 2);
+}
+
+// The fused q/k/v product of an attention layer for a small batch: qkv = x . w^T + bias, q rotated into
+// `qkv` (bf16 [M, >= heads*head_dim]), k rotated and v copied into their pages.  Same conditions and
+// return codes as tge_gemm_tcgen05_add_norm; N must be (heads + 2 * kv_heads) * head_dim.
+TGE_API int tge_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* w, long long ldw, const float* bias,
+                                      void* qkv, long long ld_qkv, int M, int N, int K, const float* cos_table,
+                                      const float* sin_table, int table_rows, int rotary, const int* positions,
+                                      const int* seq_of_token, const int* block_table, int max_pages, void* k_pages,
+                                      void* v_pages, int num_pages, int page_size, int heads, int kv_heads,
+                                      int head_dim, float* scratch, long long scratch_floats, int* status,
+                                      cudaStream_t stream) {
+  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+rope: bad sizes M=%d N=%d K=%d", M, N, K);
+  TGE_REQUIRE(N == (heads + 2 * kv_heads) * head_dim, "gemm+rope: %d weight rows are not (heads + 2 kv heads) * head_dim", N);
+  TGE_REQUIRE(rotary >= 0 && rotary <= head_dim && rotary % 2 == 0, "gemm+rope: bad rotary width %d", rotary);
+  TGE_REQUIRE(status != nullptr && page_size > 0 && max_pages > 0 && num_pages > 0, "gemm+rope: bad arguments");
+  if (M == 0) return 0;
+  if (M > FUSED_MAX_TOKENS || (size_t)N * sizeof(float) > 200 * 1024 || scratch == nullptr) return TGE_UNSUPPORTED;
+  int splits = 0;
+  int rc = launch_product(x, ldx, w, ldw, nullptr, qkv, ld_qkv, M, N, K, GEMM_STORE, scratch, scratch_floats, 0, 0, true,
+                          status, stream, &splits);
+  if (rc != 1) return rc;
+  const size_t smem = (size_t)N * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaFuncSetAttribute(splitk_qkv_rope_store_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = smem;
+  }
+  splitk_qkv_rope_store_kernel<<<M, 512, smem, stream>>>(
+      scratch, bias, (__nv_bfloat16*)qkv, ld_qkv, M, N, splits, cos_table, sin_table, table_rows, rotary, positions,
+      seq_of_token, block_table, max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size,
+      heads, kv_heads, head_dim, status);
+  return tge_launched("splitk_qkv_rope_store", 2);
 }

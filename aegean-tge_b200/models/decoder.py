@@ -106,8 +106,11 @@ class DecoderModel:
     def forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Runs the step's tokens through all layers; returns float32 logits [R, vocab] of the wanted rows."""
         x = self.embedding.forward(ctx.token_ids)
-        for index in self.spec.schedule:
-            self.blocks[index].forward(x, ctx, self.layer_caches[index])
+        schedule = self.spec.schedule
+        h = None                              # the next layer's first norm, when the previous layer produced it
+        for step, index in enumerate(schedule):
+            following = self.blocks[schedule[step + 1]].mixer_norm if step + 1 < len(schedule) else None
+            h = self.blocks[index].forward(x, ctx, self.layer_caches[index], h=h, next_norm=following)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, rows=logit_rows)

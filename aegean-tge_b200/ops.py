@@ -67,6 +67,13 @@ def core() -> ctypes.CDLL:
                                         _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                                            _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_gemm_tcgen05_add_norm", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
+                                                    _c_int, _c_ptr, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr,
+                                                    _c_ptr])
+        _declare(lib, "tge_gemm_tcgen05_qkv_rope", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
+                                                    _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                                                    _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                    _c_ptr, _c_ll, _c_ptr, _c_ptr])
         lib.tge_gemm_tcgen05_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_gemm_tcgen05_scratch_floats.restype = _c_ll
         _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
@@ -329,6 +336,89 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
     _check(lib.tge_gemm_simt(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                              int(x.dtype == torch.bfloat16), epilogue, _stream()), lib)
     return out
+
+
+FUSED_MAX_TOKENS = 256      # small batches: product + one kernel per token row; larger ones use separate kernels
+
+
+def linear_add_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], stream: torch.Tensor,
+                    norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """stream (float32 [M, N]) += x . w^T (+ bias); returns RMSNorm(stream) * norm_weight in ``out_dtype``.
+
+    For a small bfloat16 batch the partial sums of the product are added into the stream and the new
+    rows normalised by one kernel; otherwise the product and the norm run as separate kernels.
+    """
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype == torch.bfloat16 and USE_TCGEN05 and M <= FUSED_MAX_TOKENS and out_dtype == torch.bfloat16:
+        _want(x, "linear input", torch.bfloat16, contiguous=False)
+        _want(w, "linear weight", torch.bfloat16, contiguous=False)
+        _want(stream, "stream", torch.float32, contiguous=False)
+        _want(norm_weight, "norm weight", torch.float32)
+        if bias is not None:
+            _want(bias, "linear bias", torch.float32)
+        if tuple(stream.shape) != (M, N) or w.shape[1] != K or norm_weight.numel() != N:
+            raise KernelError("linear_add_norm: shapes do not fit")
+        lib = core()
+        need = max(lib.tge_gemm_tcgen05_scratch_floats(M, N, K), M * N)
+        scratch = scratch_floats(need)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        rc = lib.tge_gemm_tcgen05_add_norm(x.data_ptr(), _rows_2d(x, "linear input"), w.data_ptr(),
+                                           _rows_2d(w, "linear weight"), _ptr(bias), stream.data_ptr(),
+                                           _rows_2d(stream, "stream"), M, N, K, norm_weight.data_ptr(), float(eps),
+                                           out.data_ptr(), N, scratch.data_ptr(), scratch.numel(),
+                                           status_word().data_ptr(), _stream())
+        if _check(rc, lib) != UNSUPPORTED:
+            return out
+    linear(x, w, bias, GEMM_ADD_F32, out=stream)
+    return rmsnorm(stream, norm_weight, eps, out_dtype)
+
+
+def linear_qkv_rope_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                          sin: Optional[torch.Tensor], rotary: int, positions: torch.Tensor,
+                          seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                          v_pages: torch.Tensor, heads: int, kv_heads: int, head_dim: int) -> torch.Tensor:
+    """The fused q/k/v product of an attention layer followed by rotation and the cache store.
+
+    Returns the qkv buffer [T, (heads + 2 kv_heads) * head_dim] whose first heads*head_dim columns hold the
+    rotated queries.  For a small bfloat16 batch one kernel per token row adds the product's partial sums,
+    rotates and stores; otherwise the product and the rotate-and-store kernel run one after the other
+    (then the k and v columns of the buffer are filled as well).
+    """
+    M, K = x.shape
+    N = w.shape[0]
+    if (x.dtype == torch.bfloat16 and USE_TCGEN05 and M <= FUSED_MAX_TOKENS):
+        _want(x, "linear input", torch.bfloat16, contiguous=False)
+        _want(w, "linear weight", torch.bfloat16, contiguous=False)
+        for name, t in (("positions", positions), ("seq_of_token", seq_of_token), ("block table", block_table)):
+            _want(t, name, torch.int32)
+        _want(k_pages, "k pages", torch.bfloat16)
+        _want(v_pages, "v pages", torch.bfloat16)
+        if rotary > 0:
+            _want(cos, "cos table", torch.float32)
+            _want(sin, "sin table", torch.float32)
+        if bias is not None:
+            _want(bias, "linear bias", torch.float32)
+        num_pages, page_kv, page_size, page_hd = k_pages.shape
+        if page_kv != kv_heads or page_hd != head_dim or v_pages.shape != k_pages.shape or w.shape[1] != K:
+            raise KernelError("linear_qkv_rope_store: shapes do not fit")
+        lib = core()
+        need = max(lib.tge_gemm_tcgen05_scratch_floats(M, N, K), M * N)
+        scratch = scratch_floats(need)
+        qkv = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        rc = lib.tge_gemm_tcgen05_qkv_rope(x.data_ptr(), _rows_2d(x, "linear input"), w.data_ptr(),
+                                           _rows_2d(w, "linear weight"), _ptr(bias), qkv.data_ptr(), N, M, N, K,
+                                           _ptr(cos), _ptr(sin), 0 if cos is None else cos.shape[0], rotary,
+                                           positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+                                           block_table.shape[1], k_pages.data_ptr(), v_pages.data_ptr(), num_pages,
+                                           page_size, heads, kv_heads, head_dim, scratch.data_ptr(), scratch.numel(),
+                                           status_word().data_ptr(), _stream())
+        if _check(rc, lib) != UNSUPPORTED:
+            return qkv
+    qkv = linear(x, w, bias, GEMM_STORE)
+    rope_kv_store(qkv, cos, sin, rotary, positions, seq_of_token, block_table, k_pages, v_pages, heads, kv_heads,
+                  head_dim)
+    return qkv
 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,

@@ -93,21 +93,28 @@ class GQAttention(Mixer):
     def attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         """Everything up to, not including, the output projection: [T, heads*head_dim]."""
         ops = self.ops
-        qkv = ops.linear(h, self.w_qkv, self.b_qkv, ops.GEMM_STORE)
         k_pages, v_pages = cache.paged["k"], cache.paged["v"]
         table = ctx.block_tables[cache.group]
         tables = self.position.rotary_tables()
-        if tables is None:
-            q = qkv[:, :self.q_dim].view(-1, self.heads, self.head_dim)
-            k = qkv[:, self.q_dim:self.q_dim + self.kv_dim].view(-1, self.kv_heads, self.head_dim)
-            self.position.apply(q, k, ctx.positions)
-            cos = sin = None
-            rotary = 0
-        else:
+        if tables is not None and cache.owner:
+            # product, bias, rotation and cache store together (one or two kernels, chosen by batch size)
             cos, sin, rotary = tables
-        ops.rope_kv_store(qkv, cos, sin, rotary, ctx.positions, ctx.seq_of_token, table,
-                          k_pages if cache.owner else None, v_pages if cache.owner else None,
-                          self.heads, self.kv_heads, self.head_dim)
+            qkv = ops.linear_qkv_rope_store(h, self.w_qkv, self.b_qkv, cos, sin, rotary, ctx.positions,
+                                            ctx.seq_of_token, table, k_pages, v_pages, self.heads, self.kv_heads,
+                                            self.head_dim)
+        else:
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv, ops.GEMM_STORE)
+            if tables is None:
+                q = qkv[:, :self.q_dim].view(-1, self.heads, self.head_dim)
+                k = qkv[:, self.q_dim:self.q_dim + self.kv_dim].view(-1, self.kv_heads, self.head_dim)
+                self.position.apply(q, k, ctx.positions)
+                cos = sin = None
+                rotary = 0
+            else:
+                cos, sin, rotary = tables
+            ops.rope_kv_store(qkv, cos, sin, rotary, ctx.positions, ctx.seq_of_token, table,
+                              k_pages if cache.owner else None, v_pages if cache.owner else None,
+                              self.heads, self.kv_heads, self.head_dim)
         return ops.attention(qkv[:, :self.q_dim], k_pages, v_pages, table, ctx.q_start, ctx.start_pos, ctx.positions,
                              ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads,
                              self.kv_heads, self.head_dim, self.scale, window=int(self.window or 0),
@@ -116,5 +123,10 @@ class GQAttention(Mixer):
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         return self.ops.linear(self.attend(h, ctx, cache), self.w_o, self.b_o, self.ops.GEMM_STORE)
 
-    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
-        self.ops.linear(self.attend(h, ctx, cache), self.w_o, self.b_o, self.ops.GEMM_ADD_F32, out=x)
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache, next_norm=None):
+        a = self.attend(h, ctx, cache)
+        fused = next_norm.fusable() if next_norm is not None else None
+        if fused is not None:
+            return self.ops.linear_add_norm(a, self.w_o, self.b_o, x, fused[0], fused[1], self.env.dtype)
+        self.ops.linear(a, self.w_o, self.b_o, self.ops.GEMM_ADD_F32, out=x)
+        return None

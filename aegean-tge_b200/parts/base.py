@@ -149,6 +149,10 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def fusable(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight, eps) if this is a plain RMSNorm that a product's epilogue kernel may apply, else None."""
+        return None
+
 
 class PositionEncoding(Part):
     """Rotates or shifts queries and keys by position.
@@ -179,21 +183,29 @@ class Mixer(Part):
         """h: run dtype [T, H] (already normed) -> [T, H] to be added to the stream."""
         raise NotImplementedError
 
-    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache,
+                    next_norm: Optional["Norm"] = None) -> Optional[torch.Tensor]:
         """Adds the mixer's output to the float32 stream ``x`` in place.
 
         The default adds ``forward``'s result with the add kernel; a mixer
-        whose last product can add in its epilogue overrides this.
+        whose last product can add in its epilogue overrides this.  ``next_norm``
+        is the norm that will be applied to ``x`` next: a mixer that can apply it
+        in the same kernel returns the normed rows, everyone else returns None
+        and the caller runs the norm itself.
         """
         self.ops.add_to_stream(x, self.forward(h, ctx, cache))
+        return None
 
 
 class FeedForward(Part):
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
-    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> None:
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext,
+                    next_norm: Optional["Norm"] = None) -> Optional[torch.Tensor]:
+        """As ``Mixer.forward_add``: adds into ``x``; may return ``next_norm(x)`` if it computed it."""
         self.ops.add_to_stream(x, self.forward(h, ctx))
+        return None
 
 
 class Block:
@@ -207,7 +219,13 @@ class Block:
         self.ffn_norm = ffn_norm
         self.env = env
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache, h: Optional[torch.Tensor] = None,
+                next_norm: Optional[Norm] = None) -> Optional[torch.Tensor]:
+        """Runs the layer on the stream ``x`` in place.
+
+        ``h``: ``mixer_norm(x)`` if the previous layer already computed it.  ``next_norm``: the norm the
+        next layer will apply to ``x`` first; the block may return its result (else None).
+        """
         raise NotImplementedError
 
     def parts(self) -> Dict[str, Part]:

@@ -15,8 +15,10 @@ class PreNormBlock(Block):
     (src/models/qwen2.cpp:2055, :2099-2105, :2118).
     """
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> None:
-        h = self.mixer_norm.forward(x)
-        self.mixer.forward_add(h, x, ctx, cache)
-        h = self.ffn_norm.forward(x)
-        self.feed_forward.forward_add(h, x, ctx)
+    def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None):
+        if h is None:
+            h = self.mixer_norm.forward(x)
+        h = self.mixer.forward_add(h, x, ctx, cache, next_norm=self.ffn_norm)
+        if h is None:
+            h = self.ffn_norm.forward(x)
+        return self.feed_forward.forward_add(h, x, ctx, next_norm=next_norm)

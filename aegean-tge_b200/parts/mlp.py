@@ -47,6 +47,10 @@ class SwiGLU(FeedForward):
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
         return self.ops.linear(a, self.w_down, None, self.ops.GEMM_STORE)
 
-    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> None:
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None):
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
+        fused = next_norm.fusable() if next_norm is not None else None
+        if fused is not None:
+            return self.ops.linear_add_norm(a, self.w_down, None, x, fused[0], fused[1], self.env.dtype)
         self.ops.linear(a, self.w_down, None, self.ops.GEMM_ADD_F32, out=x)
+        return None

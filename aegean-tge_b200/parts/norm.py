@@ -37,3 +37,6 @@ class RMSNorm(Norm):
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.ops.rmsnorm(x, self.weight, self.eps, self.env.dtype, rows=rows)
+
+    def fusable(self):
+        return self.weight, self.eps
