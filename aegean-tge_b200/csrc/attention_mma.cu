@@ -112,6 +112,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [2][BKV][ROW_ELEMS]
   __nv_bfloat16* sV = sK + 2 * BKV * ROW_ELEMS;                             // [2][BKV][ROW_ELEMS]
   __shared__ int tile_info[2];
+  pdl_trigger();
+  pdl_wait();
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
@@ -332,6 +334,8 @@ constexpr int STAGE_ELEMS = 2 * BKV * ROW_ELEMS;   // K tile then V tile
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -582,6 +586,8 @@ __device__ __forceinline__ uint32_t swizzled(int row, int col) {
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ unsigned char smem_dyn[];
+  pdl_trigger();
+  pdl_wait();
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzle atoms are 1024 bytes
   unsigned char* generic = smem_dyn + (base - raw);
@@ -841,6 +847,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
                                        const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                                        int out_stride, int total_tokens, int heads, int window, int split_tokens,
                                        int num_splits) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const int pos = positions[t];
   const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
@@ -881,7 +889,7 @@ int launch(const AttnParams& p, int tiles, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(tiles, p.kv_heads, p.num_splits);
-  attention_mma_kernel<NWARPS><<<grid, NWARPS * 32, smem, stream>>>(p);
+  tge_launch(attention_mma_kernel<NWARPS>, grid, NWARPS * 32, smem, stream, p);
   return tge_check_launch("attention_mma");
 }
 
@@ -955,13 +963,13 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     }
     p.bq = 1;
     dim3 grid(num_seqs, kv_heads, num_splits);
-    attention_decode_tma_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(*map_k, *map_v, p);
+    tge_launch(attention_decode_tma_kernel, grid, DEC_WARPS * 32, smem, stream, *map_k, *map_v, p);
     int rc = tge_check_launch("attention_decode_tma");
     if (rc != 0) return rc;
     if (num_splits > 1) {
       dim3 mgrid(tokens, heads);
-      attention_merge_kernel<<<mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
-          p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+      tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
+          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -983,13 +991,13 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     }
     p.bq = 1;
     dim3 grid(num_seqs, kv_heads, num_splits);
-    attention_decode_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(p);
+    tge_launch(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, p);
     int rc = tge_check_launch("attention_decode");
     if (rc != 0) return rc;
     if (num_splits > 1) {
       dim3 mgrid(tokens, heads);
-      attention_merge_kernel<<<mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
-          p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+      tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
+          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1007,8 +1015,8 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   if (rc != 0) return rc;
   if (num_splits > 1) {
     dim3 grid(tokens, heads);
-    attention_merge_kernel<<<grid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream>>>(
-        p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+    tge_launch(attention_merge_kernel, grid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
+        (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
     return tge_launched("attention_merge", 2);
   }
   return 1;

@@ -42,6 +42,32 @@ constexpr int TGE_UNSUPPORTED = -100;  // shape outside what the kernel takes; n
     }                                     \
   } while (0)
 
+// Programmatic dependent launch.  A kernel calls pdl_trigger() as its first statement (the next kernel in
+// the stream may then be scheduled and run its own set-up) and pdl_wait() before it first touches global
+// memory that an earlier kernel writes or reads: the wait returns once the preceding kernel has finished
+// and its writes are visible.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+bool tge_pdl_enabled();
+
+// Launches `kernel` so that it may start while its predecessor in the stream drains (see above).
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t tge_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = tge_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

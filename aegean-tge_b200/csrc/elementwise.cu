@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * hidden;
@@ -31,9 +33,9 @@ TGE_API int tge_embedding(const void* table, int is_bf16, const int* ids, float*
               tokens, hidden, vocab);
   if (tokens == 0) return 0;
   if (is_bf16)
-    embedding_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+    tge_launch(embedding_kernel<__nv_bfloat16>, tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
   else
-    embedding_kernel<float><<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
+    tge_launch(embedding_kernel<float>, tokens, 256, 0, stream, (const float*)table, ids, out, hidden, vocab, status);
   return tge_launched("embedding", 1);
 }
 
@@ -47,6 +49,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows, TOut* __restrict__ out, int hidden,
                                int src_rows, float eps, int* status) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   int src = rows ? rows[r] : r;
   if (src < 0 || src >= src_rows) {
@@ -72,9 +76,9 @@ TGE_API int tge_rmsnorm(const float* x, const float* weight, const int* rows, vo
   if (out_rows == 0) return 0;
   const int threads = hidden >= 2048 ? 512 : 256;
   if (out_is_bf16)
-    rmsnorm_kernel<__nv_bfloat16><<<out_rows, threads, 0, stream>>>(x, weight, rows, (__nv_bfloat16*)out, hidden, src_rows, eps, status);
+    tge_launch(rmsnorm_kernel<__nv_bfloat16>, out_rows, threads, 0, stream, x, weight, rows, (__nv_bfloat16*)out, hidden, src_rows, eps, status);
   else
-    rmsnorm_kernel<float><<<out_rows, threads, 0, stream>>>(x, weight, rows, (float*)out, hidden, src_rows, eps, status);
+    tge_launch(rmsnorm_kernel<float>, out_rows, threads, 0, stream, x, weight, rows, (float*)out, hidden, src_rows, eps, status);
   return tge_launched("rmsnorm", 1);
 }
 
@@ -114,6 +118,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, const 
                                      const int* __restrict__ block_table, int max_pages, T* __restrict__ k_pages,
                                      T* __restrict__ v_pages, int num_pages, int page_size, int heads, int kv_heads,
                                      int head_dim, int rotary, int store_kv, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   T* row = qkv + (size_t)t * row_stride;
@@ -176,12 +182,12 @@ TGE_API int tge_rope_kv_store(void* qkv, int is_bf16, int row_stride, const floa
   TGE_REQUIRE(row_stride >= (heads + (store_kv ? 2 * kv_heads : 0)) * head_dim, "rope_kv_store: row stride %d too small", row_stride);
   if (tokens == 0) return 0;
   if (is_bf16)
-    rope_kv_store_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(
+    tge_launch(rope_kv_store_kernel<__nv_bfloat16>, tokens, 256, 0, stream,
         (__nv_bfloat16*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table,
         max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim,
         rotary, store_kv, status);
   else
-    rope_kv_store_kernel<float><<<tokens, 256, 0, stream>>>(
+    tge_launch(rope_kv_store_kernel<float>, tokens, 256, 0, stream,
         (float*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table, max_pages,
         (float*)k_pages, (float*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, rotary, store_kv, status);
   return tge_launched("rope_kv_store", 1);

@@ -25,6 +25,7 @@
 // TGE_STATUS_WAIT_TIMEOUT in the status word, all roles leave their loops, the
 // loader waits (bounded) for its copies in flight, tensor memory is freed and
 // the kernel returns.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
@@ -190,6 +191,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // Only now may the next kernel be scheduled: this block already holds its tensor memory, so a block of
+  // the next kernel that lands on the same SM can at worst wait for it, never starve it.
+  pdl_trigger();
+  pdl_wait();   // set-up above overlapped the previous kernel; from here on its results are read
 
   const int total_work = p.tiles_w * p.tiles_t * p.splits;
 
@@ -329,6 +334,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // Adds the k-splits in split order and applies the epilogue.
 __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const float* __restrict__ bias, void* out,
                                        long long ldo, int m_tok, int n_w, int splits, int epilogue) {
+  pdl_trigger();
+  pdl_wait();
   const size_t plane = (size_t)m_tok * n_w;
   if (epilogue == GEMM_SWIGLU) {
     const size_t count = plane / 2;
@@ -517,42 +524,80 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   }
   const long long total = (long long)p.tiles_w * p.tiles_t * p.splits;
   const int grid = (int)(total < sm_count() ? total : sm_count());
-  gemm_tcgen05_kernel<<<grid, NUM_THREADS, smem, stream>>>(map_w, map_x, p);
+  tge_launch(gemm_tcgen05_kernel, grid, NUM_THREADS, smem, stream, map_w, map_x, p);
   rc = tge_check_launch("gemm_tcgen05");
   if (rc != 0) return rc;
   *splits_out = to_partial ? plan.splits : 0;
   return 1;
 }
 
-// One block per token: stream[t, :] += sum of the k-split partial sums (+ bias), then RMSNorm of the
-// new row (same summation pattern as the stand-alone norm kernel) into norm_out.
-__global__ void splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
-                                       float* __restrict__ stream, long long ld_stream,
-                                       const float* __restrict__ norm_weight, float eps,
-                                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w,
-                                       int splits) {
-  extern __shared__ float row_values[];
+// A cluster of NORM_CLUSTER blocks per token: block r owns a slice of the row's columns.  Each adds the
+// k-split partial sums (+ bias) into the float32 stream, the slices' sums of squares meet through
+// distributed shared memory (added in rank order), and each block writes its slice of
+// RMSNorm(row) * weight.  Eight blocks per row keep a decode step's handful of rows from running on a
+// handful of SMs.
+constexpr int NORM_CLUSTER = 8;
+constexpr int NORM_THREADS = 128;
+constexpr int NORM_PER_THREAD = 8;               // columns per thread: rows up to 8 * 128 * 8 = 8192 wide
+
+__global__ void __cluster_dims__(NORM_CLUSTER, 1, 1) __launch_bounds__(NORM_THREADS)
+splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ stream,
+                       long long ld_stream, const float* __restrict__ norm_weight, float eps,
+                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w, int splits,
+                       int slice) {
   __shared__ float scratch[32];
-  const int t = blockIdx.x;
+  __shared__ float slice_sums[NORM_CLUSTER];       // every block receives every slice's sum of squares
+  pdl_trigger();
+  cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+  // first half of a cluster barrier: its second half, below, proves that every block of the cluster is
+  // running before anyone writes into a neighbour's shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  const int rank = blockIdx.x, t = blockIdx.y;
+  const int begin = min(rank * slice, n_w), end = min(begin + slice, n_w);
   const size_t plane = (size_t)m_tok * n_w;
+  // constants of the model first: they do not depend on the previous kernel
+  float gain[NORM_PER_THREAD], add[NORM_PER_THREAD], value[NORM_PER_THREAD];
+#pragma unroll
+  for (int i = 0; i < NORM_PER_THREAD; ++i) {
+    const int n = begin + threadIdx.x + i * NORM_THREADS;
+    gain[i] = n < end ? norm_weight[n] : 0.0f;
+    add[i] = (bias && n < end) ? bias[n] : 0.0f;
+  }
+  pdl_wait();
   float sum = 0.0f;
-  for (int n = threadIdx.x; n < n_w; n += blockDim.x) {
-    float acc = 0.0f;
-    for (int s = 0; s < splits; ++s) acc += partial[s * plane + (size_t)t * n_w + n];
-    if (bias) acc += bias[n];
-    const float v = stream[(size_t)t * ld_stream + n] + acc;
-    stream[(size_t)t * ld_stream + n] = v;
-    row_values[n] = v;
-    sum = fmaf(v, v, sum);
+#pragma unroll
+  for (int i = 0; i < NORM_PER_THREAD; ++i) {
+    const int n = begin + threadIdx.x + i * NORM_THREADS;
+    value[i] = 0.0f;
+    if (n < end) {
+      const float* src = partial + (size_t)t * n_w + n;
+      float acc = 0.0f;
+#pragma unroll 4
+      for (int s = 0; s < splits; ++s) acc += src[s * plane];
+      const float v = stream[(size_t)t * ld_stream + n] + (acc + add[i]);
+      stream[(size_t)t * ld_stream + n] = v;
+      value[i] = v;
+      sum = fmaf(v, v, sum);
+    }
   }
   sum = block_sum(sum, scratch);
-  const float scale = 1.0f / sqrtf(sum / (float)n_w + eps);
-  for (int n = threadIdx.x; n < n_w; n += blockDim.x)
-    norm_out[(size_t)t * ld_norm + n] = __float2bfloat16_rn(row_values[n] * scale * norm_weight[n]);
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+  if (threadIdx.x < NORM_CLUSTER) *cluster.map_shared_rank(&slice_sums[rank], threadIdx.x) = sum;
+  cluster.sync();                                  // one meeting point: after it everybody reads only its own memory
+  float total = 0.0f;
+#pragma unroll
+  for (int r = 0; r < NORM_CLUSTER; ++r) total += slice_sums[r];
+  const float scale = 1.0f / sqrtf(total / (float)n_w + eps);
+#pragma unroll
+  for (int i = 0; i < NORM_PER_THREAD; ++i) {
+    const int n = begin + threadIdx.x + i * NORM_THREADS;
+    if (n < end) norm_out[(size_t)t * ld_norm + n] = __float2bfloat16_rn(value[i] * scale * gain[i]);
+  }
 }
 
-// One block per token: q, k, v = sum of the partial sums + bias; q rotated into the qkv buffer, k rotated
-// and v copied into their pages (formulas as in the stand-alone rotate-and-store kernel).
+// One block per (token, head): the head's q, k or v values = sum of the partial sums + bias; a query head is
+// rotated into the qkv buffer, a key head rotated into its page, a value head copied into its page
+// (formulas as in the stand-alone rotate-and-store kernel).
 __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
                                              __nv_bfloat16* __restrict__ qkv, long long ld_qkv, int m_tok, int n_w,
                                              int splits, const float* __restrict__ cos_table,
@@ -562,50 +607,52 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
                                              __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                                              int num_pages, int page_size, int heads, int kv_heads, int head_dim,
                                              int* status) {
-  extern __shared__ float row_values[];
-  const int t = blockIdx.x;
+  extern __shared__ float head_values[];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, unit = blockIdx.y;     // unit: query heads, then key heads, then value heads
   const size_t plane = (size_t)m_tok * n_w;
-  for (int n = threadIdx.x; n < n_w; n += blockDim.x) {
+  const int column0 = unit * head_dim;
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    const float* src = partial + (size_t)t * n_w + column0 + d;
     float acc = 0.0f;
-    for (int s = 0; s < splits; ++s) acc += partial[s * plane + (size_t)t * n_w + n];
-    if (bias) acc += bias[n];
-    row_values[n] = acc;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) acc += src[s * plane];
+    if (bias) acc += bias[column0 + d];
+    head_values[d] = acc;
   }
   __syncthreads();
   const int pos = positions[t];
   const int half = rotary / 2;
-  if (half > 0 && (pos < 0 || pos >= table_rows)) {
+  const bool is_value = unit >= heads + kv_heads;
+  if (!is_value && half > 0 && (pos < 0 || pos >= table_rows)) {
     if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
     return;
   }
   const float* cs = cos_table + (size_t)pos * half;
   const float* sn = sin_table + (size_t)pos * half;
-  auto rotated = [&](const float* head, int d) -> float {
-    if (d < half) return head[d] * cs[d] - head[d + half] * sn[d];
-    if (d < rotary) return head[d - half] * sn[d - half] + head[d] * cs[d - half];
-    return head[d];
+  auto rotated = [&](int d) -> float {
+    if (is_value) return head_values[d];
+    if (d < half) return head_values[d] * cs[d] - head_values[d + half] * sn[d];
+    if (d < rotary) return head_values[d - half] * sn[d - half] + head_values[d] * cs[d - half];
+    return head_values[d];
   };
-  __nv_bfloat16* q_out = qkv + (size_t)t * ld_qkv;
-  for (int i = threadIdx.x; i < heads * head_dim; i += blockDim.x) {
-    const int h = i / head_dim, d = i - h * head_dim;
-    q_out[i] = __float2bfloat16_rn(rotated(row_values + (size_t)h * head_dim, d));
+  if (unit < heads) {
+    __nv_bfloat16* dst = qkv + (size_t)t * ld_qkv + column0;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = __float2bfloat16_rn(rotated(d));
+    return;
   }
   const int seq = seq_of_token[t];
   const int page_index = pos / page_size;
-  const int page = page_index < max_pages ? block_table[(size_t)seq * max_pages + page_index] : -1;
+  const int page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
   if (page < 0 || page >= num_pages) {
     if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
     return;
   }
-  const int slot = pos - page_index * page_size;
-  const float* k_row = row_values + (size_t)heads * head_dim;
-  const float* v_row = k_row + (size_t)kv_heads * head_dim;
-  for (int i = threadIdx.x; i < kv_heads * head_dim; i += blockDim.x) {
-    const int h = i / head_dim, d = i - h * head_dim;
-    const size_t dst = (((size_t)page * kv_heads + h) * page_size + slot) * head_dim + d;
-    k_pages[dst] = __float2bfloat16_rn(rotated(k_row + (size_t)h * head_dim, d));
-    v_pages[dst] = __float2bfloat16_rn(v_row[i]);
-  }
+  const int h = is_value ? unit - heads - kv_heads : unit - heads;
+  __nv_bfloat16* dst = (is_value ? v_pages : k_pages) +
+                       (((size_t)page * kv_heads + h) * page_size + (pos - page_index * page_size)) * head_dim;
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = __float2bfloat16_rn(rotated(d));
 }
 
 constexpr int FUSED_MAX_TOKENS = 256;   // above this the product's own epilogue is the better path
@@ -635,7 +682,7 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
     const long long count = epilogue == GEMM_SWIGLU ? (long long)M * N / 2 : (long long)M * N;
     long long blocks = (count + 255) / 256;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
-    splitk_epilogue_kernel<<<(int)blocks, 256, 0, stream>>>(scratch, bias, out, ldo, M, N, splits, epilogue);
+    tge_launch(splitk_epilogue_kernel, (int)blocks, 256, 0, stream, (const float*)scratch, bias, out, ldo, M, N, splits, epilogue);
     return tge_launched("splitk_epilogue", 2);
   }
   return 1;
@@ -652,19 +699,16 @@ TGE_API int tge_gemm_tcgen05_add_norm(const void* x, long long ldx, const void* 
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+norm: bad sizes M=%d N=%d K=%d", M, N, K);
   TGE_REQUIRE(status != nullptr && norm_weight != nullptr && norm_out != nullptr && eps > 0.0f, "gemm+norm: bad arguments");
   if (M == 0) return 0;
-  if (M > FUSED_MAX_TOKENS || (size_t)N * sizeof(float) > 200 * 1024 || scratch == nullptr) return TGE_UNSUPPORTED;
+  if (M > FUSED_MAX_TOKENS || N > NORM_CLUSTER * NORM_THREADS * NORM_PER_THREAD || scratch == nullptr) return TGE_UNSUPPORTED;
   int splits = 0;
   int rc = launch_product(x, ldx, w, ldw, nullptr, stream_out, ldo, M, N, K, GEMM_ADD_F32, scratch, scratch_floats, 0, 0,
                           true, status, stream, &splits);
   if (rc != 1) return rc;
-  const size_t smem = (size_t)N * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaFuncSetAttribute(splitk_add_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    configured = smem;
-  }
-  splitk_add_norm_kernel<<<M, N >= 2048 ? 512 : 256, smem, stream>>>(scratch, bias, stream_out, ldo, norm_weight, eps,
-                                                                   (__nv_bfloat16*)norm_out, ld_norm, M, N, splits);
+  int slice = (N + NORM_CLUSTER - 1) / NORM_CLUSTER;
+  slice = (slice + 3) / 4 * 4;
+  tge_launch(splitk_add_norm_kernel, dim3(NORM_CLUSTER, M), NORM_THREADS, 0, stream,
+             (const float*)scratch, bias, stream_out, ldo, norm_weight, eps, (__nv_bfloat16*)norm_out, ld_norm, M, N,
+             splits, slice);
   return tge_launched("splitk_add_norm", 2);
 }
 
@@ -688,15 +732,9 @@ TGE_API int tge_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* 
   int rc = launch_product(x, ldx, w, ldw, nullptr, qkv, ld_qkv, M, N, K, GEMM_STORE, scratch, scratch_floats, 0, 0, true,
                           status, stream, &splits);
   if (rc != 1) return rc;
-  const size_t smem = (size_t)N * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    cudaFuncSetAttribute(splitk_qkv_rope_store_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    configured = smem;
-  }
-  splitk_qkv_rope_store_kernel<<<M, 512, smem, stream>>>(
-      scratch, bias, (__nv_bfloat16*)qkv, ld_qkv, M, N, splits, cos_table, sin_table, table_rows, rotary, positions,
-      seq_of_token, block_table, max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size,
-      heads, kv_heads, head_dim, status);
+  tge_launch(splitk_qkv_rope_store_kernel, dim3(M, heads + 2 * kv_heads), head_dim >= 128 ? 128 : 64,
+             (size_t)head_dim * sizeof(float), stream, (const float*)scratch, bias, (__nv_bfloat16*)qkv, ld_qkv, M, N,
+             splits, cos_table, sin_table, table_rows, rotary, positions, seq_of_token, block_table, max_pages,
+             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, status);
   return tge_launched("splitk_qkv_rope_store", 2);
 }

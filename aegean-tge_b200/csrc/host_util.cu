@@ -3,6 +3,7 @@
 // a negative code; the Python binding raises it.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -22,6 +23,15 @@ int tge_check_launch(const char* what) {
     return -2;
   }
   return 0;
+}
+
+bool tge_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* off = getenv("TGE_NO_PDL");
+    enabled = (off != nullptr && off[0] != '\0') ? 0 : 1;
+  }
+  return enabled == 1;
 }
 
 TGE_API const char* tge_last_error() { return g_error; }

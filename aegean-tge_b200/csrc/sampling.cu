@@ -33,6 +33,8 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   __shared__ float segment_sum[32];
   __shared__ int chosen_segment;
   __shared__ float chosen_target;
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* z = logits + (size_t)row * row_stride;
@@ -132,6 +134,6 @@ TGE_API int tge_sample(const float* logits, long long row_stride, const float* t
   TGE_REQUIRE(rows >= 0 && vocab > 0, "sample: bad sizes rows=%d vocab=%d", rows, vocab);
   TGE_REQUIRE(row_stride >= vocab, "sample: row stride %lld shorter than the vocabulary %d", row_stride, vocab);
   if (rows == 0) return 0;
-  sample_kernel<<<rows, 1024, 0, stream>>>(logits, row_stride, temperature, uniform, out, vocab);
+  tge_launch(sample_kernel, rows, 1024, 0, stream, logits, row_stride, temperature, uniform, out, vocab);
   return tge_launched("sample", 1);
 }
