@@ -801,6 +801,263 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------
+// Prompt portions for head sizes that are multiples of 64: eight warps own 128 rows ((query, head-of-group)
+// pairs of one kv head), every warp takes 16 rows against the whole 64-position tile, tiles arrive by TMA as
+// in the decode kernel.  Tiles that lie wholly before every row's position need no mask; the accumulator is
+// rescaled only when a running maximum moved.
+// ---------------------------------------------------------------------------
+constexpr int PRE_WARPS = 8;
+
+__global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ int tile_info[2];
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* generic = smem_dyn + (base - raw);
+  const uint32_t bars = base + DEC_STAGES * TMA_STAGE_BYTES;
+  int* local_table = reinterpret_cast<int*>(generic + DEC_STAGES * TMA_STAGE_BYTES + 64);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int kvh = blockIdx.y, split = blockIdx.z;
+  if (tid == 0) {
+    int remaining = blockIdx.x, seq = -1, tile = 0;
+    for (int s = 0; s < p.num_seqs; ++s) {
+      const int q_len = p.q_start[s + 1] - p.q_start[s];
+      const int tiles = (q_len + p.bq - 1) / p.bq;
+      if (remaining < tiles) { seq = s; tile = remaining; break; }
+      remaining -= tiles;
+    }
+    tile_info[0] = seq;
+    tile_info[1] = tile;
+  }
+  __syncthreads();
+  const int seq = tile_info[0];
+  if (seq < 0) return;
+  const int q_first = tile_info[1] * p.bq;
+  const int q_begin = p.q_start[seq];
+  const int q_len = p.q_start[seq + 1] - q_begin;
+  const int q_count = min(p.bq, q_len - q_first);
+  const int pos0 = p.start_pos[seq] + q_first;
+
+  int lo = p.window > 0 ? max(pos0 - p.window + 1, 0) : 0;
+  int hi = pos0 + q_count;
+  if (p.num_splits > 1) {
+    lo = max(lo, split * p.split_tokens);
+    hi = min(hi, (split + 1) * p.split_tokens);
+  }
+  if (lo >= hi) return;
+
+  const int k_first = lo / BKV * BKV;
+  const int num_tiles = (hi - k_first + BKV - 1) / BKV;
+  const int first_page = k_first >> p.page_shift;
+  const int last_page = (k_first + num_tiles * BKV - 1) >> p.page_shift;
+  for (int i = first_page + tid; i <= last_page; i += PRE_WARPS * 32) {
+    int page = i < p.max_pages ? p.block_table[(size_t)seq * p.max_pages + i] : -1;
+    if (page >= p.num_pages) page = -2;
+    local_table[i - first_page] = page;
+  }
+  {
+    uint4* fill = reinterpret_cast<uint4*>(generic);
+    for (int i = tid; i < DEC_STAGES * TMA_STAGE_BYTES / 16; i += PRE_WARPS * 32) fill[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  __syncthreads();
+
+  const int pages_per_tile = BKV >> p.page_shift;
+  auto issue = [&](int tile) {
+    const int stage = tile % DEC_STAGES;
+    const uint32_t k_dst = base + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
+    const uint32_t bar = bars + 8 * stage;
+    int boxes = 0;
+    for (int j = 0; j < pages_per_tile; ++j) {
+      const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
+      if (page >= 0 && (k_first + tile * BKV + (j << p.page_shift)) < hi) ++boxes;
+    }
+    mbar_expect_tx(bar, (uint32_t)boxes * 2u * TMA_BLOCKS * (uint32_t)(p.page_size * 128));
+    for (int j = 0; j < pages_per_tile; ++j) {
+      const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
+      if (page < 0 || (k_first + tile * BKV + (j << p.page_shift)) >= hi) continue;
+      const int row = (page * p.kv_heads + kvh) << p.page_shift;
+#pragma unroll
+      for (int b = 0; b < TMA_BLOCKS; ++b) {
+        const uint32_t offset = (uint32_t)(b * (BKV * 128) + (j << p.page_shift) * 128);
+        tma_load_2d(k_dst + offset, &map_k, bar, b * 64, row);
+        tma_load_2d(v_dst + offset, &map_v, bar, b * 64, row);
+      }
+    }
+  };
+  if (tid == 0) {
+    for (int s = 0; s < DEC_STAGES - 1 && s < num_tiles; ++s) issue(s);
+  }
+
+  int row_token[2], row_pos[2], row_head[2];
+  bool row_valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + g8 + 8 * i;
+    const int qi = r / p.group, gg = r - qi * p.group;
+    row_valid[i] = qi < q_count;
+    row_token[i] = q_begin + q_first + (row_valid[i] ? qi : 0);
+    row_pos[i] = pos0 + qi;
+    row_head[i] = kvh * p.group + gg;
+  }
+  // the warp's rows span these positions (for skipping masks and whole tiles)
+  const int warp_q_lo = (warp * 16) / p.group, warp_q_hi = min((warp * 16 + 15) / p.group, q_count - 1);
+  const bool warp_active = warp_q_lo < q_count;
+  const int warp_pos_lo = pos0 + warp_q_lo, warp_pos_hi = pos0 + warp_q_hi;
+
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const __nv_bfloat16* src = p.q + (size_t)row_token[i] * p.q_stride + (size_t)row_head[i] * HD + kc * 16 + 2 * t4;
+      qf[kc][i] = row_valid[i] ? *reinterpret_cast<const uint32_t*>(src) : 0u;
+      qf[kc][i + 2] = row_valid[i] ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
+    }
+  }
+  float o_acc[HD / 8][4];
+#pragma unroll
+  for (int d = 0; d < HD / 8; ++d)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o_acc[d][e] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  bool bad_page = false;
+
+  for (int it = 0; it < num_tiles; ++it) {
+    __syncthreads();
+    if (tid == 0 && it + DEC_STAGES - 1 < num_tiles) issue(it + DEC_STAGES - 1);
+    const int stage = it % DEC_STAGES;
+    mbar_wait_bounded(bars + 8 * stage, (uint32_t)(it / DEC_STAGES) & 1u, p.status);
+    const uint32_t tK = base + stage * TMA_STAGE_BYTES, tV = tK + TMA_TILE_BYTES;
+    const int k0 = k_first + it * BKV;
+    // nothing in this tile is visible to this warp's rows: before their windows or after their positions
+    if (!warp_active || k0 > warp_pos_hi) continue;
+    if (p.window > 0 && k0 + BKV <= warp_pos_lo - p.window + 1) continue;
+    if (local_table[(max(k0, lo) >> p.page_shift) - first_page] < 0) bad_page = true;
+
+    float s_acc[BKV / 8][4];
+#pragma unroll
+    for (int n = 0; n < BKV / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_acc[n][e] = 0.0f;
+#pragma unroll
+    for (int kc = 0; kc < HD / 16; ++kc) {
+#pragma unroll
+      for (int nt = 0; nt < BKV / 8; nt += 2) {
+        const int mi = lane >> 3;
+        const int n = (nt + (mi >> 1)) * 8 + (lane & 7);
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4(tK + swizzled(n, kc * 16 + (mi & 1) * 8), r0, r1, r2, r3);
+        mma_bf16(s_acc[nt], qf[kc], r0, r1);
+        mma_bf16(s_acc[nt + 1], qf[kc], r2, r3);
+      }
+    }
+    // a tile wholly inside [lo, hi), before every row's position and inside every row's window needs no mask
+    const bool clean = k0 >= lo && k0 + BKV <= hi && k0 + BKV - 1 <= warp_pos_lo &&
+                       (p.window == 0 || k0 >= warp_pos_hi - p.window + 1) && warp_q_hi < q_count &&
+                       (warp * 16 + 15) / p.group < q_count;
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int first_key = p.window > 0 ? row_pos[i] - p.window + 1 : 0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < BKV / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float sv = s_acc[n][2 * i + e] * p.scale_log2;
+          if (!clean) {
+            const int kpos = k0 + n * 8 + 2 * t4 + e;
+            const bool visible = row_valid[i] && kpos <= row_pos[i] && kpos >= first_key && kpos >= lo && kpos < hi;
+            sv = visible ? sv : -INFINITY;
+          }
+          s_acc[n][2 * i + e] = sv;
+          mx = fmaxf(mx, sv);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[i], mx);
+      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
+      corr[i] = exp2f(m_run[i] - m_use);
+      float sum = 0.0f;
+#pragma unroll
+      for (int n = 0; n < BKV / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float pv = exp2f(s_acc[n][2 * i + e] - m_use);
+          s_acc[n][2 * i + e] = pv;
+          sum += pv;
+        }
+      }
+      l_run[i] = l_run[i] * corr[i] + sum;
+      m_run[i] = m_new;
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d) {
+        o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
+        o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < BKV / 16; ++kk) {
+      uint32_t pf[4];
+      pf[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
+      pf[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
+      pf[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
+      pf[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
+#pragma unroll
+      for (int dt = 0; dt < HD / 8; dt += 2) {
+        const int mi = lane >> 3;
+        const int key = kk * 16 + (mi & 1) * 8 + (lane & 7);
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4_trans(tV + swizzled(key, (dt + (mi >> 1)) * 8), r0, r1, r2, r3);
+        mma_bf16(o_acc[dt], pf, r0, r1);
+        mma_bf16(o_acc[dt + 1], pf, r2, r3);
+      }
+    }
+  }
+  if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+    l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!row_valid[i]) continue;
+    if (p.num_splits == 1) {
+      const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+      __nv_bfloat16* dst = p.out + (size_t)row_token[i] * p.out_stride + (size_t)row_head[i] * HD;
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d)
+        *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * t4) = pack_bf16(o_acc[d][2 * i] * inv, o_acc[d][2 * i + 1] * inv);
+    } else {
+      const size_t slot = ((size_t)split * p.total_tokens + row_token[i]) * p.heads + row_head[i];
+      float* dst = p.partial_o + slot * HD;
+#pragma unroll
+      for (int d = 0; d < HD / 8; ++d)
+        *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o_acc[d][2 * i], o_acc[d][2 * i + 1]);
+      if (t4 == 0) {
+        p.partial_ml[slot * 2] = m_run[i];
+        p.partial_ml[slot * 2 + 1] = l_run[i];
+      }
+    }
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1002,6 +1259,40 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     }
     return 1;
   }
+#if TGE_HEAD_DIM % 64 == 0
+  if (max_q_len > 1 && group <= 64 && page_size >= 8) {
+    const CUtensorMap* map_k = pool_map(k_pages, num_pages, kv_heads, page_size);
+    const CUtensorMap* map_v = pool_map(v_pages, num_pages, kv_heads, page_size);
+    if (!map_k || !map_v) return -3;
+    p.bq = (PRE_WARPS * 16) / group;
+    const int range = (num_splits > 1 ? p.split_tokens : max_ctx_len) + 2 * BKV;
+    const size_t smem = 1024 + (size_t)DEC_STAGES * TMA_STAGE_BYTES + 64 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
+    if (smem <= 227 * 1024) {
+      static size_t configured = 0;
+      if (smem > configured) {
+        cudaError_t err = cudaFuncSetAttribute(attention_prefill_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+          tge_set_error("attention_prefill: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+          return -2;
+        }
+        configured = smem;
+      }
+      const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;
+      dim3 grid(tiles, kv_heads, num_splits);
+      tge_launch(attention_prefill_tma_kernel, grid, PRE_WARPS * 32, smem, stream, *map_k, *map_v, p);
+      int rc = tge_check_launch("attention_prefill_tma");
+      if (rc != 0) return rc;
+      if (num_splits > 1) {
+        dim3 mgrid(tokens, heads);
+        tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
+                   (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
+                   window, p.split_tokens, num_splits);
+        return tge_launched("attention_merge", 2);
+      }
+      return 1;
+    }
+  }
+#endif
   // rows per block: one warp (16 rows) per block when every portion is a single token and the group fits
   int nwarps = 4;
   if (max_q_len <= 1) nwarps = group <= 16 ? 1 : (group <= 32 ? 2 : 4);
