@@ -807,9 +807,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
 // in the decode kernel.  Tiles that lie wholly before every row's position need no mask; the accumulator is
 // rescaled only when a running maximum moved.
 // ---------------------------------------------------------------------------
-constexpr int PRE_WARPS = 8;
+constexpr int PRE_WARPS = 8;                  // warps that compute; one more warp issues the TMA loads
+constexpr int PRE_STAGES = 4;
+constexpr int PRE_THREADS = (PRE_WARPS + 1) * 32;
 
-__global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ int tile_info[2];
@@ -818,15 +824,19 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* generic = smem_dyn + (base - raw);
-  const uint32_t bars = base + DEC_STAGES * TMA_STAGE_BYTES;
-  int* local_table = reinterpret_cast<int*>(generic + DEC_STAGES * TMA_STAGE_BYTES + 64);
+  const uint32_t bars = base + PRE_STAGES * TMA_STAGE_BYTES;            // full[stages], then empty[stages]
+  int* local_table = reinterpret_cast<int*>(generic + PRE_STAGES * TMA_STAGE_BYTES + 128);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g8 = lane >> 2, t4 = lane & 3;
   const int kvh = blockIdx.y, split = blockIdx.z;
   if (tid == 0) {
-    int remaining = blockIdx.x, seq = -1, tile = 0;
-    for (int s = 0; s < p.num_seqs; ++s) {
+    // Blocks take tiles from the back: under a causal mask the later tiles of a portion are the longer ones,
+    // and starting them first keeps the tail of the launch short.
+    int total = 0;
+    for (int s = 0; s < p.num_seqs; ++s) total += (p.q_start[s + 1] - p.q_start[s] + p.bq - 1) / p.bq;
+    int remaining = total - 1 - (int)blockIdx.x, seq = -1, tile = 0;
+    for (int s = 0; s < p.num_seqs && remaining >= 0; ++s) {
       const int q_len = p.q_start[s + 1] - p.q_start[s];
       const int tiles = (q_len + p.bq - 1) / p.bq;
       if (remaining < tiles) { seq = s; tile = remaining; break; }
@@ -856,17 +866,20 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
   const int num_tiles = (hi - k_first + BKV - 1) / BKV;
   const int first_page = k_first >> p.page_shift;
   const int last_page = (k_first + num_tiles * BKV - 1) >> p.page_shift;
-  for (int i = first_page + tid; i <= last_page; i += PRE_WARPS * 32) {
+  for (int i = first_page + tid; i <= last_page; i += PRE_THREADS) {
     int page = i < p.max_pages ? p.block_table[(size_t)seq * p.max_pages + i] : -1;
     if (page >= p.num_pages) page = -2;
     local_table[i - first_page] = page;
   }
   {
     uint4* fill = reinterpret_cast<uint4*>(generic);
-    for (int i = tid; i < DEC_STAGES * TMA_STAGE_BYTES / 16; i += PRE_WARPS * 32) fill[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < PRE_STAGES * TMA_STAGE_BYTES / 16; i += PRE_THREADS) fill[i] = make_uint4(0, 0, 0, 0);
   }
   if (tid == 0) {
-    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(bars + 8 * s, 1);
+    for (int s = 0; s < PRE_STAGES; ++s) {
+      mbar_init(bars + 8 * s, 1);
+      mbar_init(bars + 8 * (PRE_STAGES + s), PRE_WARPS);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -874,7 +887,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
 
   const int pages_per_tile = BKV >> p.page_shift;
   auto issue = [&](int tile) {
-    const int stage = tile % DEC_STAGES;
+    const int stage = tile % PRE_STAGES;
     const uint32_t k_dst = base + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
     const uint32_t bar = bars + 8 * stage;
     int boxes = 0;
@@ -895,8 +908,16 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
       }
     }
   };
-  if (tid == 0) {
-    for (int s = 0; s < DEC_STAGES - 1 && s < num_tiles; ++s) issue(s);
+  if (warp == PRE_WARPS) {
+    // the loading warp: a stage is refilled as soon as all eight computing warps have released it
+    if (lane == 0) {
+      for (int tile = 0; tile < num_tiles; ++tile) {
+        if (tile >= PRE_STAGES)
+          mbar_wait_bounded(bars + 8 * (PRE_STAGES + tile % PRE_STAGES), (uint32_t)(tile / PRE_STAGES - 1) & 1u, p.status);
+        issue(tile);
+      }
+    }
+    return;
   }
 
   int row_token[2], row_pos[2], row_head[2];
@@ -934,15 +955,17 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
   bool bad_page = false;
 
   for (int it = 0; it < num_tiles; ++it) {
-    __syncthreads();
-    if (tid == 0 && it + DEC_STAGES - 1 < num_tiles) issue(it + DEC_STAGES - 1);
-    const int stage = it % DEC_STAGES;
-    mbar_wait_bounded(bars + 8 * stage, (uint32_t)(it / DEC_STAGES) & 1u, p.status);
+    const int stage = it % PRE_STAGES;
+    mbar_wait_bounded(bars + 8 * stage, (uint32_t)(it / PRE_STAGES) & 1u, p.status);
     const uint32_t tK = base + stage * TMA_STAGE_BYTES, tV = tK + TMA_TILE_BYTES;
     const int k0 = k_first + it * BKV;
-    // nothing in this tile is visible to this warp's rows: before their windows or after their positions
-    if (!warp_active || k0 > warp_pos_hi) continue;
-    if (p.window > 0 && k0 + BKV <= warp_pos_lo - p.window + 1) continue;
+    // nothing in this tile is visible to this warp's rows (before their windows or after their positions):
+    // release the stage at once
+    const bool skip = !warp_active || k0 > warp_pos_hi || (p.window > 0 && k0 + BKV <= warp_pos_lo - p.window + 1);
+    if (skip) {
+      if (lane == 0) mbar_arrive(bars + 8 * (PRE_STAGES + stage));
+      continue;
+    }
     if (local_table[(max(k0, lo) >> p.page_shift) - first_page] < 0) bad_page = true;
 
     float s_acc[BKV / 8][4];
@@ -1027,6 +1050,8 @@ __global__ void __launch_bounds__(PRE_WARPS * 32) attention_prefill_tma_kernel(
         mma_bf16(o_acc[dt + 1], pf, r2, r3);
       }
     }
+    __syncwarp();                                        // the whole warp has read the stage
+    if (lane == 0) mbar_arrive(bars + 8 * (PRE_STAGES + stage));
   }
   if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
 
@@ -1266,7 +1291,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     if (!map_k || !map_v) return -3;
     p.bq = (PRE_WARPS * 16) / group;
     const int range = (num_splits > 1 ? p.split_tokens : max_ctx_len) + 2 * BKV;
-    const size_t smem = 1024 + (size_t)DEC_STAGES * TMA_STAGE_BYTES + 64 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
+    const size_t smem = 1024 + (size_t)PRE_STAGES * TMA_STAGE_BYTES + 128 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
     if (smem <= 227 * 1024) {
       static size_t configured = 0;
       if (smem > configured) {
@@ -1279,7 +1304,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
       }
       const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;
       dim3 grid(tiles, kv_heads, num_splits);
-      tge_launch(attention_prefill_tma_kernel, grid, PRE_WARPS * 32, smem, stream, *map_k, *map_v, p);
+      tge_launch(attention_prefill_tma_kernel, grid, PRE_THREADS, smem, stream, *map_k, *map_v, p);
       int rc = tge_check_launch("attention_prefill_tma");
       if (rc != 0) return rc;
       if (num_splits > 1) {
