@@ -27,6 +27,7 @@
 // the kernel returns.
 #include <cooperative_groups.h>
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -39,7 +40,8 @@ constexpr int BK = 64;                   // k per stage: 64 bf16 = one 128-byte 
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 8;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;              // two per 32-lane quarter of tensor memory, each taking half the columns
+constexpr int NUM_THREADS = (2 + EPI_WARPS) * 32;
 constexpr int SMEM_LIMIT = 227 * 1024;
 
 struct GemmParams {
@@ -177,7 +179,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 4);
+      mbar_init(tempty_bar(s), EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -271,6 +273,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   } else {
     // ------------------------------- epilogue -------------------------------
     const int quarter = warp & 3;            // tensor-memory lanes this warp may read
+    const int column_half = (warp - 2) >> 2; // which half of the token columns it takes
+    const int c_begin = p.bn >= 32 ? column_half * (p.bn / 2) : 0;
+    const int c_end = p.bn >= 32 ? c_begin + p.bn / 2 : (column_half == 0 ? p.bn : 0);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -283,7 +288,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int n = tile_w * BM + quarter * 32 + lane;          // weight row = output feature
       const bool n_ok = n < p.n_w;
       const float bias = (p.bias && n_ok && !p.to_partial) ? p.bias[n] : 0.0f;
-      for (int c0 = 0; c0 < p.bn; c0 += 16) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 16) {
         uint32_t r[16];
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.bn + c0);
         tc_load16(taddr, r);
@@ -300,16 +305,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + __uint_as_float(r[j]) + bias;
           continue;
         }
+        if (!p.to_partial && p.epilogue == GEMM_SWIGLU) {
+          // Even lanes hold gate rows, odd lanes the matching up rows.  Per pair of token columns one
+          // exchange gives the even lane (gate, up) of the first column and the odd lane those of the second.
+          const bool odd = lane & 1;
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const float a = __uint_as_float(r[j]) + bias, b = __uint_as_float(r[j + 1]) + bias;
+            const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+            const float g = odd ? got : a, u = odd ? b : got;
+            const int m = m0 + j + (odd ? 1 : 0);
+            if (n_ok && m < p.m_tok)
+              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
+                  __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
+          }
+          continue;
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = m0 + j;
           float v = __uint_as_float(r[j]) + bias;
           if (p.to_partial) {
             if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
-          } else if (p.epilogue == GEMM_SWIGLU) {
-            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-            if (n_ok && m < p.m_tok && (lane & 1) == 0)
-              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_mul(v, other));
           } else if (n_ok && m < p.m_tok) {
             if (p.epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
             else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
@@ -443,6 +460,7 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   const int k_blocks = (K + BK - 1) / BK;
   if (stages > k_blocks) stages = k_blocks < 2 ? 2 : k_blocks;
+  if (getenv("TGE_GEMM_STAGES")) { const int forced = atoi(getenv("TGE_GEMM_STAGES")); if (forced >= 2 && forced < stages) stages = forced; }
   plan.stages = stages;
   const long long tiles = (long long)tiles_w * ((M + bn - 1) / bn);
   int splits = 1;
