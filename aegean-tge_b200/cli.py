@@ -285,6 +285,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             return replay_main(["--model", args.model, "--dtype", args.dtype, "--out", args.out,
                                 "--max-tokens", str(args.max_tokens)])
         raise UsageError(f"unknown command {args.command}")
+    except SystemExit as stop:          # argparse prints --help itself and leaves through here
+        return int(stop.code or 0)
     except UsageError as error:
         print(str(error), file=sys.stderr)
         return 2
