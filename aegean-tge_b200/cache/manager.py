@@ -24,6 +24,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import LayerCache, PagedCacheSpec, StateSpec
@@ -259,6 +260,14 @@ class CacheManager:
         self._free_slots.append(self._slot_of.pop(request))
         del self._tokens[request]
         del self._computed[request]
+
+    def fill_block_table(self, group_index: int, requests: Sequence[Hashable], out: "np.ndarray") -> None:
+        """Writes the requests' page ids into ``out`` (int32 [len(requests), width]), NO_PAGE beyond each row's end."""
+        group = self.groups[group_index]
+        out.fill(NO_PAGE)
+        for row, request in enumerate(requests):
+            table = group.tables[request]
+            out[row, :len(table)] = table
 
     def block_table(self, group_index: int, requests: Sequence[Hashable], width: Optional[int] = None) -> List[List[int]]:
         """Rows of physical page ids, padded with NO_PAGE to a common width."""

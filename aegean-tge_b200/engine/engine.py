@@ -131,7 +131,8 @@ class Engine:
         if sampling_items:
             sampled = self.sampler.sample(logits, [item.request.sampling for item in sampling_items],
                                           [item.request.rng for item in sampling_items],
-                                          [item.request.tokens for item in sampling_items])
+                                          [item.request.tokens if item.request.sampling.has_penalty else ()
+                                           for item in sampling_items])
             self.d2h_bytes_last = 4 * len(sampled)
         return self.scheduler.update(plan, sampled)
 

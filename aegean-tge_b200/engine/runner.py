@@ -90,8 +90,7 @@ class ModelRunner:
             graph = self._graphs.get((batch, bound))
             if graph is None:
                 graph = self._graphs[(batch, bound)] = DecodeGraph(self, batch, bound)
-            tables = [self.cache.block_table(g, requests, width=graph.width) for g in range(len(self.cache.groups))]
-            logits = graph.run([int(p.tokens[0]) for p in portions], starts, slots, tables)
+            logits = graph.run(self.cache, requests, [int(p.tokens[0]) for p in portions], starts, slots)
             self.ops.launches += graph.kernels
             self.h2d_bytes_last = graph.nbytes
             self.graph_replays += 1
@@ -149,6 +148,7 @@ class DecodeGraph:
         self.dev = torch.zeros(cursor, dtype=torch.int32, device=device)
         view = lambda t, name: t[self.offsets[name][0]:self.offsets[name][0] + self.offsets[name][1]]
         self.hs = [{name: view(host, name) for name, _ in sizes} for host in self.hosts]
+        self.np_hs = [{name: tensor.numpy() for name, tensor in h.items()} for h in self.hs]   # same memory, cheap to fill
         d = {name: view(self.dev, name) for name, _ in sizes}
         for h in self.hs:
             # constants of a decode step
@@ -183,20 +183,20 @@ class DecodeGraph:
         self.kernels = ops.launches - before
         ops.launches = before
 
-    def run(self, tokens, positions, slots, tables) -> torch.Tensor:
+    def run(self, cache: CacheManager, requests, tokens, positions, slots) -> torch.Tensor:
         turn = self.turn
         self.turn = (turn + 1) % self.ring
         if self.copied[turn] is not None:
             self.copied[turn].synchronize()
-        h = self.hs[turn]
-        h["token_ids"].copy_(torch.tensor(tokens, dtype=torch.int32))
-        pos = torch.tensor(positions, dtype=torch.int32)
-        h["positions"].copy_(pos)
-        h["start_pos"].copy_(pos)
-        h["ctx_len"].copy_(pos + 1)
-        h["slots"].copy_(torch.tensor(slots, dtype=torch.int32))
-        for g, table in enumerate(tables):
-            h[f"table{g}"].copy_(torch.tensor(table, dtype=torch.int32).view(-1))
+        h = self.np_hs[turn]
+        h["token_ids"][:] = tokens
+        h["positions"][:] = positions
+        h["start_pos"][:] = positions
+        h["ctx_len"][:] = positions
+        h["ctx_len"] += 1
+        h["slots"][:] = slots
+        for g in range(len(cache.groups)):
+            cache.fill_block_table(g, requests, h[f"table{g}"].reshape(self.batch, self.width))
         self.dev.copy_(self.hosts[turn], non_blocking=True)
         event = torch.cuda.Event()
         event.record()

@@ -62,6 +62,15 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """Tokens [start, start + count) of prompt-then-output, without building the whole list."""
+        split = len(self.prompt)
+        if start >= split:
+            return self.output[start - split:start - split + count]
+        if start + count <= split:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - split]
+
 
 @dataclass
 class ScheduledPortion:
@@ -83,7 +92,7 @@ class StepPlan:
     def portions(self) -> List[Portion]:
         out = []
         for item in self.items:
-            tokens = item.request.tokens[item.start:item.start + item.count]
+            tokens = item.request.token_slice(item.start, item.count)
             out.append(Portion(item.request.id, tokens, [item.count - 1] if item.samples else []))
         return out
 

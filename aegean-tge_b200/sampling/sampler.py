@@ -23,6 +23,7 @@ class Sampler:
     def __init__(self, ops, device: torch.device):
         self.ops = ops
         self.device = device
+        self._zeros = {}            # rows -> float32 zeros [2, rows] on the device (greedy: temperature 0, no draw)
 
     def _to_device(self, values, dtype) -> torch.Tensor:
         host = torch.tensor(values, dtype=dtype)
@@ -58,7 +59,12 @@ class Sampler:
             scores = self.ops.apply_penalty(logits, self._to_device(flat or [0], torch.int32),
                                             self._to_device(starts, torch.int32),
                                             self._to_device([float(p.repeat_penalty) for p in params], torch.float32))
-        floats = self._to_device([temperatures, uniforms], torch.float32)
+        if all(p.greedy for p in params):
+            if rows not in self._zeros:
+                self._zeros[rows] = torch.zeros((2, rows), dtype=torch.float32, device=self.device)
+            floats = self._zeros[rows]
+        else:
+            floats = self._to_device([temperatures, uniforms], torch.float32)
         cut_rows = [i for i, p in enumerate(params) if p.has_cuts and not p.greedy]
         if not cut_rows:
             return self.ops.sample(scores, floats[0], floats[1]).cpu().tolist()
