@@ -36,7 +36,15 @@ TINY_C = {
     "tie_word_embeddings": False, "max_position_embeddings": 384, "use_sliding_window": False,
     "hidden_act": "silu",
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2)}
+# tiny D: head_dim 64 (the TMA-fed attention kernels), 8 query heads on 2 kv heads, long positions
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 8, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 320, "vocab_size": 500, "rope_theta": 100000.0, "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096, "use_sliding_window": False,
+    "hidden_act": "silu",
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 
 def pytest_configure(config):

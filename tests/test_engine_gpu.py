@@ -10,7 +10,7 @@ from plain import qwen2_plain as plain
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-MODELS = ["A", "B", "C"]
+MODELS = ["A", "B", "C", "D"]
 
 
 def _tokens(name, count, salt=0):
@@ -220,3 +220,50 @@ def test_kernels_are_loaded_and_cpu_is_refused(model_dirs):
     assert "libtge_core.so" in names and "libtge_attn_hd16.so" in names
     with pytest.raises(ops.KernelError):
         ops.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-6, torch.float32)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_context_in_portions_then_decoding(model_dirs, oracle, dtype):
+    """1,500 positions: prompt portions of 600 (several key splits and page-table staging), then tokens one by one."""
+    name = "D"
+    tokens = _tokens(name, 1500, salt=9)
+    ref = oracle(name, tokens)
+    engine = _engine(model_dirs, name, dtype, context=2048, max_tokens=2048)
+    rows = []
+    for begin in (0, 600, 1200):
+        count = min(600, 1480 - begin)
+        rows.append(engine.runner.step([_portion("r", tokens[begin:begin + count], want=[count - 1])]))
+    for t in range(1480, 1500):
+        rows.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
+    got = torch.cat(rows)
+    want = ref[[599, 1199, 1479] + list(range(1480, 1500))]
+    assert rel_error(got, want) < MODEL_TOL[dtype]
+
+
+def test_tensor_core_and_cuda_core_paths_agree_at_a_large_layer_shape():
+    """A two-layer model with the layer sizes of a 14B model (hidden 5120, 40 heads on 8 kv heads of 128,
+    feed-forward 13824): bfloat16 logits through the tcgen05/TMA kernels against the CUDA-core kernels."""
+    from aegean_tge_b200 import Engine, ops
+    config = {"architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 5120,
+              "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 13824,
+              "vocab_size": 3000, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+              "max_position_embeddings": 1024}
+    rnd = random.Random(4)
+    tokens = [rnd.randrange(3000) for _ in range(300)]
+    engine = Engine(random_config=config, seed=5, dtype="bfloat16", context=512, max_tokens=1024, max_requests=4)
+
+    def run():
+        out = [engine.runner.step([_portion("r", tokens[:280], want=[279, 0])])]
+        for t in range(280, 300):
+            out.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
+        engine.runner.finish("r")
+        return torch.cat(out).float().cpu()
+    fast = run()
+    ops.USE_TCGEN05, ops.USE_MMA_ATTENTION = False, False
+    engine.runner.use_graphs = False            # a captured graph would replay the kernels it was captured with
+    try:
+        slow = run()
+    finally:
+        ops.USE_TCGEN05, ops.USE_MMA_ATTENTION = True, True
+    ops.check_status()
+    assert rel_error(fast, slow) < MODEL_TOL["bfloat16"]
