@@ -18,6 +18,8 @@
 // when t <= p and, with a window w > 0, t > p - w.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <map>
 #include <tuple>
 
@@ -1083,6 +1085,8 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
   }
 }
 
+#include "attention_tc.cuh"
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1291,6 +1295,34 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     if (!map_k || !map_v) return -3;
     p.bq = (PRE_WARPS * 16) / group;
     const int range = (num_splits > 1 ? p.split_tokens : max_ctx_len) + 2 * BKV;
+    static const bool use_tc = getenv("TGE_NO_TC_ATTENTION") == nullptr || getenv("TGE_NO_TC_ATTENTION")[0] == '\0';
+    if (use_tc && tc::smem_bytes(range >> p.page_shift) <= 227 * 1024 && q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 &&
+        out_stride % 8 == 0 && (uintptr_t)out % 16 == 0) {
+      // the tcgen05 kernel: 128 rows per block as well
+      const size_t smem = tc::smem_bytes(range >> p.page_shift);
+      static size_t configured_tc = 0;
+      if (smem > configured_tc) {
+        cudaError_t err = cudaFuncSetAttribute(tc::attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) {
+          tge_set_error("attention_prefill_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+          return -2;
+        }
+        configured_tc = smem;
+      }
+      const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;
+      dim3 grid(tiles, kv_heads, num_splits);
+      tge_launch(tc::attention_prefill_tc_kernel, grid, tc::THREADS, smem, stream, *map_k, *map_v, p);
+      int rc = tge_check_launch("attention_prefill_tc");
+      if (rc != 0) return rc;
+      if (num_splits > 1) {
+        dim3 mgrid(tokens, heads);
+        tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
+                   (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
+                   window, p.split_tokens, num_splits);
+        return tge_launched("attention_merge", 2);
+      }
+      return 1;
+    }
     const size_t smem = 1024 + (size_t)PRE_STAGES * TMA_STAGE_BYTES + 128 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
     if (smem <= 227 * 1024) {
       static size_t configured = 0;
