@@ -26,7 +26,7 @@ constexpr int STAGES = 2;
 constexpr int Q_BYTES = ROWS * HD * 2;
 constexpr int P_BYTES = ROWS * BKV * 2;            // 16 KiB
 constexpr bool P_OVER_K = TMA_TILE_BYTES >= P_BYTES;   // P reuses the K tile of its stage when that is large enough
-constexpr int TMEM_COLS = (BKV + HD) <= 128 ? 128 : 256;
+constexpr int TMEM_COLS = (2 * BKV + HD) <= 128 ? 128 : 256;        // two score buffers and the output
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -49,8 +49,8 @@ __device__ __forceinline__ void load32(uint32_t taddr, uint32_t r[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
+__device__ __forceinline__ void wait_loads() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 __device__ __forceinline__ void store32(uint32_t taddr, const uint32_t r[32]) {
   asm volatile(
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   const uint32_t p_own = base + Q_BYTES;                                   // used only when P does not fit over K
   const uint32_t stages = base + Q_BYTES + (P_OVER_K ? 0 : P_BYTES);
   const uint32_t bars = stages + STAGES * TMA_STAGE_BYTES;
-  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, s_bar = bars + 16 * STAGES, p_bar = s_bar + 8, o_bar = s_bar + 16;
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, s_bar = bars + 16 * STAGES, p_bar = s_bar + 16, o_bar = s_bar + 24;   // s_bar: one per score buffer
   int* local_table = reinterpret_cast<int*>(generic + (stages - base) + STAGES * TMA_STAGE_BYTES + 64);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       mbar_init(empty_bar + 8 * s, 1);
     }
     mbar_init(s_bar, 1);
+    mbar_init(s_bar + 8, 1);
     mbar_init(p_bar, 4);
     mbar_init(o_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   fence_after();
   const uint32_t tmem_base = tmem_slot;
   pdl_trigger();                                                      // tensor memory is held: the next kernel may be scheduled
-  const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + BKV;
+  const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + 2 * BKV;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -201,28 +202,31 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       };
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
-      issue_loads(0);
-      for (int it = 0; it < num_tiles; ++it) {
-        const int stage = it % STAGES;
-        if (it + 1 < num_tiles) {
-          if (it + 1 >= STAGES)
-            mbar_wait_bounded(empty_bar + 8 * ((it + 1) % STAGES), (uint32_t)((it + 1) / STAGES - 1) & 1u, p.status);
-          issue_loads(it + 1);
-        }
-        mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)(it / STAGES) & 1u, p.status);
+      // S = Q K^T of one tile into score buffer (tile & 1)
+      auto issue_scores = [&](int tile) {
+        const int stage = tile % STAGES;
+        mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)(tile / STAGES) & 1u, p.status);
         fence_after();
-        const uint32_t k_tile = stages + stage * TMA_STAGE_BYTES, v_tile = k_tile + TMA_TILE_BYTES;
-        // S = Q K^T over the head dimension, 16 at a time
+        const uint32_t k_tile = stages + stage * TMA_STAGE_BYTES;
+        const uint32_t d_tmem = s_tmem + (uint32_t)((tile & 1) * BKV);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t block = ks >> 2, step = ks & 3;
-          mma(s_tmem, desc_k_major(q_smem + block * (ROWS * 128) + step * 32),
+          mma(d_tmem, desc_k_major(q_smem + block * (ROWS * 128) + step * 32),
               desc_k_major(k_tile + block * (BKV * 128) + step * 32), idesc_s, ks > 0 ? 1u : 0u);
         }
-        commit(s_bar);
+        commit(s_bar + 8 * (tile & 1));
+      };
+      issue_loads(0);
+      if (num_tiles > 1) issue_loads(1);
+      issue_scores(0);
+      for (int it = 0; it < num_tiles; ++it) {
+        const int stage = it % STAGES;
+        // the next tile's scores are computed while the softmax warps work on this tile's
+        if (it + 1 < num_tiles) issue_scores(it + 1);
         mbar_wait_bounded(p_bar, (uint32_t)it & 1u, p.status);
         fence_after();
-        // O_tile = P V over the 64 positions, 16 at a time
+        const uint32_t k_tile = stages + stage * TMA_STAGE_BYTES, v_tile = k_tile + TMA_TILE_BYTES;
         const uint32_t p_tile = P_OVER_K ? k_tile : p_own;
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks)
@@ -230,6 +234,11 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
               (it > 0 || ks > 0) ? 1u : 0u);
         commit(o_bar);
         commit(empty_bar + 8 * stage);
+        if (it + STAGES < num_tiles) {
+          // this tile's stage is free once its product has been read: refill it for tile it + 2
+          mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(it / STAGES) & 1u, p.status);
+          issue_loads(it + STAGES);
+        }
       }
     }
   } else {
@@ -244,12 +253,14 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
     for (int it = 0; it < num_tiles; ++it) {
       const int stage = it % STAGES;
       const int k0 = k_first + it * BKV;
-      mbar_wait_bounded(s_bar, (uint32_t)it & 1u, p.status);
+      mbar_wait_bounded(s_bar + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, p.status);
       fence_after();
       if (local_table[(max(k0, lo) >> p.page_shift) - first_page] < 0) bad_page = true;
       uint32_t s_bits[BKV];
-      load32(s_tmem + lane_base, s_bits);
-      load32(s_tmem + lane_base + 32, s_bits + 32);
+      const uint32_t s_now = s_tmem + (uint32_t)((it & 1) * BKV);
+      load32(s_now + lane_base, s_bits);
+      load32(s_now + lane_base + 32, s_bits + 32);
+      wait_loads();
       // a tile that every row of the warp sees whole needs no mask
       const bool whole = row_valid && k0 + BKV - 1 <= row_pos && k0 >= first_key && k0 >= lo && k0 + BKV <= hi;
       float mx = -INFINITY;
@@ -272,6 +283,11 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       const float shift = -m_use * p.scale_log2;
       float sum = 0.0f;
       const uint32_t p_row = (P_OVER_K ? stages + stage * TMA_STAGE_BYTES : p_own) + r * 128;
+      if (!P_OVER_K && it > 0) {
+        // P has one buffer of its own here: the previous tile's product must have read it
+        mbar_wait_bounded(o_bar, (uint32_t)(it - 1) & 1u, p.status);
+        fence_after();
+      }
 #pragma unroll
       for (int c = 0; c < BKV / 8; ++c) {
         float pv[8];
@@ -298,6 +314,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
           for (int c = 0; c < HD / 32; ++c) {
             uint32_t o_bits[32];
             load32(o_tmem + lane_base + c * 32, o_bits);
+            wait_loads();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o_bits[e] = __float_as_uint(__uint_as_float(o_bits[e]) * factor);
             store32(o_tmem + lane_base + c * 32, o_bits);
@@ -317,6 +334,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
     for (int c = 0; c < HD / 32; ++c) {
       uint32_t o_bits[32];
       load32(o_tmem + lane_base + c * 32, o_bits);           // every lane takes part in the load; only valid rows store
+      wait_loads();
       if (!row_valid) continue;
       if (p.num_splits == 1) {
         uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row_token * p.out_stride + (size_t)row_head * HD + c * 32);
