@@ -69,12 +69,80 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<TOut>(in[i] * scale * weight[i]);
 }
 
+// The same with 16-byte loads and the row held in registers between the two passes:
+// hidden a multiple of 4 and at most 16 values per thread.
+constexpr int NORM_VEC_ITERS = 4;
+
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(512) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                          const int* __restrict__ rows, TOut* __restrict__ out,
+                                                          int hidden, int src_rows, float eps, int* status) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int quads = hidden >> 2;
+  float4 gain[NORM_VEC_ITERS], value[NORM_VEC_ITERS];
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_ITERS; ++k) {      // constants of the model: before the wait
+    const int i = threadIdx.x + k * blockDim.x;
+    gain[k] = i < quads ? reinterpret_cast<const float4*>(weight)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const int r = blockIdx.x;
+  int src = rows ? rows[r] : r;
+  if (src < 0 || src >= src_rows) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+    src = 0;
+  }
+  const float4* in = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+  float sum = 0.0f;
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_ITERS; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    value[k] = i < quads ? in[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    sum = fmaf(value[k].x, value[k].x, sum);
+    sum = fmaf(value[k].y, value[k].y, sum);
+    sum = fmaf(value[k].z, value[k].z, sum);
+    sum = fmaf(value[k].w, value[k].w, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = 1.0f / sqrtf(sum / (float)hidden + eps);
+  TOut* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int k = 0; k < NORM_VEC_ITERS; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < quads)
+      store4(dst + 4 * (size_t)i, value[k].x * scale * gain[k].x, value[k].y * scale * gain[k].y,
+             value[k].z * scale * gain[k].z, value[k].w * scale * gain[k].w);
+  }
+}
+
 TGE_API int tge_rmsnorm(const float* x, const float* weight, const int* rows, void* out, int out_is_bf16,
                         int out_rows, int src_rows, int hidden, float eps, int* status, cudaStream_t stream) {
   TGE_REQUIRE(out_rows >= 0 && hidden > 0 && src_rows >= 0, "rmsnorm: bad sizes rows=%d hidden=%d", out_rows, hidden);
   TGE_REQUIRE(eps > 0.0f, "rmsnorm: eps must be positive");
   if (out_rows == 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : 256;
+  int threads = hidden >= 2048 ? 512 : 256;
+  const bool aligned = ((uintptr_t)x | (uintptr_t)weight | (uintptr_t)out) % 16 == 0;
+  if (hidden % 4 == 0 && hidden / 4 <= NORM_VEC_ITERS * threads && aligned) {
+    // more and smaller blocks per SM keep more loads in flight while others sit in their reduction
+    if (hidden / 4 <= NORM_VEC_ITERS * 256) threads = 256;
+    if (out_is_bf16)
+      tge_launch(rmsnorm_vec_kernel<__nv_bfloat16>, out_rows, threads, 0, stream, x, weight, rows, (__nv_bfloat16*)out, hidden, src_rows, eps, status);
+    else
+      tge_launch(rmsnorm_vec_kernel<float>, out_rows, threads, 0, stream, x, weight, rows, (float*)out, hidden, src_rows, eps, status);
+    return tge_launched("rmsnorm", 1);
+  }
   if (out_is_bf16)
     tge_launch(rmsnorm_kernel<__nv_bfloat16>, out_rows, threads, 0, stream, x, weight, rows, (__nv_bfloat16*)out, hidden, src_rows, eps, status);
   else
@@ -170,6 +238,104 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, int row_stride, const 
   }
 }
 
+// bfloat16 with everything a multiple of 8 elements: units of 16 bytes.  A unit is either a rotation
+// (8 low and the 8 matching high elements of a q or k head) or a plain copy (v, and the tail of a k head
+// beyond the rotary width).  Same formulas as above.
+__device__ __forceinline__ void unpack8(const uint4& raw, float f[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 v = __bfloat1622float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float f[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return raw;
+}
+
+__global__ void rope_kv_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride, const float* __restrict__ cos_table,
+                                         const float* __restrict__ sin_table, int table_rows,
+                                         const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                         const int* __restrict__ block_table, int max_pages,
+                                         __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                                         int num_pages, int page_size, int heads, int kv_heads, int head_dim, int rotary,
+                                         int store_kv, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+  const int half = rotary / 2;
+  const int rot_units = half / 8, tail_units = (head_dim - rotary) / 8, dim_units = head_dim / 8;
+  const int q_units = heads * rot_units;
+  const int k_rot_units = store_kv ? kv_heads * rot_units : 0;
+  const int k_tail_units = store_kv ? kv_heads * tail_units : 0;
+  const int v_units = store_kv ? kv_heads * dim_units : 0;
+  const int rotations = q_units + k_rot_units;
+  const int total = rotations + k_tail_units + v_units;
+  for (int u = threadIdx.x; u < total; u += blockDim.x) {
+    // where the unit comes from depends on nothing that has to be looked up: ask for the data first,
+    // then walk the chain position -> page
+    int h, d;
+    const __nv_bfloat16* src;
+    __nv_bfloat16* page_base;      // k or v pages for units that go to the cache
+    const bool rotation = u < rotations, is_q = u < q_units;
+    if (rotation) {
+      const int v = is_q ? u : u - q_units;
+      h = v / rot_units; d = (v - h * rot_units) * 8;
+      src = row + (size_t)(is_q ? h : heads + h) * head_dim + d;
+      page_base = k_pages;
+    } else if (u < rotations + k_tail_units) {
+      const int v = u - rotations;
+      h = v / tail_units; d = rotary + (v - h * tail_units) * 8;
+      src = row + (size_t)(heads + h) * head_dim + d;
+      page_base = k_pages;
+    } else {
+      const int v = u - rotations - k_tail_units;
+      h = v / dim_units; d = (v - h * dim_units) * 8;
+      src = row + (size_t)(heads + kv_heads + h) * head_dim + d;
+      page_base = v_pages;
+    }
+    const uint4 first = *reinterpret_cast<const uint4*>(src);
+    uint4 second = first;
+    if (rotation) second = *reinterpret_cast<const uint4*>(src + half);
+    const int pos = positions[t];
+    if (rotation && (pos < 0 || pos >= table_rows)) {
+      atomicOr(status, TGE_STATUS_BAD_ROW);
+      continue;
+    }
+    __nv_bfloat16* dst = row + (size_t)h * head_dim + d;
+    if (!is_q) {
+      const int page = block_table[(size_t)seq_of_token[t] * max_pages + pos / page_size];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, TGE_STATUS_BAD_PAGE);
+        continue;
+      }
+      dst = page_base + (((size_t)page * kv_heads + h) * page_size + pos % page_size) * head_dim + d;
+    }
+    if (!rotation) {
+      *reinterpret_cast<uint4*>(dst) = first;
+      continue;
+    }
+    const float* cs = cos_table + (size_t)pos * half + d;
+    const float* sn = sin_table + (size_t)pos * half + d;
+    float lo[8], hi[8], c[8], s[8], out_lo[8], out_hi[8];
+    *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cs);
+    *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cs + 4);
+    *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(sn);
+    *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(sn + 4);
+    unpack8(first, lo);
+    unpack8(second, hi);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      out_lo[i] = lo[i] * c[i] - hi[i] * s[i];
+      out_hi[i] = lo[i] * s[i] + hi[i] * c[i];
+    }
+    *reinterpret_cast<uint4*>(dst) = pack8(out_lo);
+    *reinterpret_cast<uint4*>(dst + half) = pack8(out_hi);
+  }
+}
+
 TGE_API int tge_rope_kv_store(void* qkv, int is_bf16, int row_stride, const float* cos_table, const float* sin_table,
                               int table_rows, const int* positions, const int* seq_of_token, const int* block_table,
                               int max_pages, void* k_pages, void* v_pages, int num_pages, int page_size, int tokens,
@@ -181,6 +347,20 @@ TGE_API int tge_rope_kv_store(void* qkv, int is_bf16, int row_stride, const floa
   TGE_REQUIRE(!store_kv || (page_size > 0 && max_pages > 0 && num_pages > 0), "rope_kv_store: bad page geometry");
   TGE_REQUIRE(row_stride >= (heads + (store_kv ? 2 * kv_heads : 0)) * head_dim, "rope_kv_store: row stride %d too small", row_stride);
   if (tokens == 0) return 0;
+  const bool by_sixteen_bytes = is_bf16 && rotary % 16 == 0 && head_dim % 8 == 0 && row_stride % 8 == 0 &&
+                                ((uintptr_t)qkv | (uintptr_t)cos_table | (uintptr_t)sin_table) % 16 == 0 &&
+                                (!store_kv || ((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0);
+  if (by_sixteen_bytes) {
+    const int units = heads * (rotary / 16) + (store_kv ? kv_heads * (rotary / 16 + (head_dim - rotary) / 8 + head_dim / 8) : 0);
+    int threads = (units + 31) / 32 * 32;
+    if (threads > 512) threads = 512;
+    if (threads < 32) threads = 32;
+    tge_launch(rope_kv_store_vec_kernel, tokens, threads, 0, stream,
+        (__nv_bfloat16*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table,
+        max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim,
+        rotary, store_kv, status);
+    return tge_launched("rope_kv_store", 1);
+  }
   if (is_bf16)
     tge_launch(rope_kv_store_kernel<__nv_bfloat16>, tokens, 256, 0, stream,
         (__nv_bfloat16*)qkv, row_stride, cos_table, sin_table, table_rows, positions, seq_of_token, block_table,

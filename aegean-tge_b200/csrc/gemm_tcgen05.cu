@@ -196,7 +196,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   // Only now may the next kernel be scheduled: this block already holds its tensor memory, so a block of
   // the next kernel that lands on the same SM can at worst wait for it, never starve it.
   pdl_trigger();
-  pdl_wait();   // set-up above overlapped the previous kernel; from here on its results are read
+  // Set-up above overlapped the previous kernel; from here on its results are read.  The loading warp
+  // waits later: weights are nobody's result, so it first asks for a ring-full of weight tiles.
+  if (warp != 0) pdl_wait();
 
   const int total_work = p.tiles_w * p.tiles_t * p.splits;
 
@@ -207,6 +209,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       uint32_t phase = 0;
       int issued = 0;
       bool ok = true;
+      int ahead = 0;      // stages of the first item whose weight tile is already on its way
+      if ((int)blockIdx.x < total_work) {
+        const int split = (int)blockIdx.x % p.splits;
+        const int tile_w = ((int)blockIdx.x / p.splits) / p.tiles_t;
+        const int kb_begin = (int)((long long)split * p.k_blocks / p.splits);
+        const int kb_end = (int)((long long)(split + 1) * p.k_blocks / p.splits);
+        ahead = kb_end - kb_begin < p.stages ? kb_end - kb_begin : p.stages;
+        for (int s = 0; s < ahead; ++s) {
+          mbar_expect_tx(full_bar(s), stage_bytes);
+          tma_load_2d(base + (uint32_t)s * stage_bytes, &map_w, full_bar(s), (kb_begin + s) * BK, tile_w * BM);
+        }
+      }
+      pdl_wait();
       for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
         const int split = work % p.splits;
         const int rest = work / p.splits;
@@ -214,10 +229,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int kb_begin = (int)((long long)split * p.k_blocks / p.splits);
         const int kb_end = (int)((long long)(split + 1) * p.k_blocks / p.splits);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
           const uint32_t a_dst = base + (uint32_t)stage * stage_bytes;
-          mbar_expect_tx(full_bar(stage), stage_bytes);
-          tma_load_2d(a_dst, &map_w, full_bar(stage), kb * BK, tile_w * BM);
+          if (ahead > 0) {
+            --ahead;      // first pass over the ring: the stage is free and its weight tile was requested above
+          } else {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
+            mbar_expect_tx(full_bar(stage), stage_bytes);
+            tma_load_2d(a_dst, &map_w, full_bar(stage), kb * BK, tile_w * BM);
+          }
           tma_load_2d(a_dst + A_STAGE_BYTES, &map_x, full_bar(stage), kb * BK, tile_t * p.bn);
           ++issued;
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -274,8 +293,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ------------------------------- epilogue -------------------------------
     const int quarter = warp & 3;            // tensor-memory lanes this warp may read
     const int column_half = (warp - 2) >> 2; // which half of the token columns it takes
-    const int c_begin = p.bn >= 32 ? column_half * (p.bn / 2) : 0;
-    const int c_end = p.bn >= 32 ? c_begin + p.bn / 2 : (column_half == 0 ? p.bn : 0);
+    const int first_half = ((p.bn / 16 + 1) / 2) * 16;   // groups of 16 columns, the odd one to the first half
+    const int c_begin = column_half == 0 ? 0 : first_half;
+    const int c_end = column_half == 0 ? first_half : p.bn;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -447,12 +467,20 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   else if (M <= 64) bn = 64;
   else if (M <= 128) bn = 128;
   else {
-    // fewer, fuller waves win: compare the time of both tilings in units of "128 columns on one SM"
-    const long long t256 = (long long)tiles_w * ((M + 255) / 256);
-    const long long t128 = (long long)tiles_w * ((M + 127) / 128);
-    const long long cost256 = (t256 + sms - 1) / sms * 2;
-    const long long cost128 = (t128 + sms - 1) / sms;
-    bn = cost128 < cost256 ? 128 : 256;
+    // Fewer, fuller waves win.  For every count of token tiles whose width (a multiple of 16) lies in
+    // 128..256 the time is waves x (columns per tile + a fixed cost per tile, in columns); ties go to
+    // the wider tile.  3584 weight rows x 2048 tokens: 8 tiles of 256 are 224 items, two waves of 272;
+    // 10 tiles of 208 are 280 items, two waves of 224.
+    const int per_tile = 16;
+    long long best = -1;
+    bn = 256;
+    for (int count = (M + 255) / 256;; ++count) {
+      const int width = ((M + count - 1) / count + 15) / 16 * 16;
+      if (width < 128) break;
+      const long long items = (long long)tiles_w * ((M + width - 1) / width);
+      const long long cost = (items + sms - 1) / sms * (width + per_tile);
+      if (best < 0 || cost < best) { best = cost; bn = width; }
+    }
   }
   plan.bn = bn;
   const int stage_bytes = A_STAGE_BYTES + bn * BK * 2;
@@ -460,7 +488,6 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   const int k_blocks = (K + BK - 1) / BK;
   if (stages > k_blocks) stages = k_blocks < 2 ? 2 : k_blocks;
-  if (getenv("TGE_GEMM_STAGES")) { const int forced = atoi(getenv("TGE_GEMM_STAGES")); if (forced >= 2 && forced < stages) stages = forced; }
   plan.stages = stages;
   const long long tiles = (long long)tiles_w * ((M + bn - 1) / bn);
   int splits = 1;

@@ -41,7 +41,8 @@ def test_embedding_bad_token_is_reported_not_read(ops):
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,hidden,eps", [(5, 72, 1e-6), (3, 200, 1e-5), (2, 3000, 3e-6), (1, 5120, 1e-6)])
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 72, 1e-6), (3, 200, 1e-5), (2, 3000, 3e-6), (1, 5120, 1e-6),
+                                             (3, 70, 1e-6), (2, 9004, 1e-6), (300, 3584, 1e-6)])
 def test_rmsnorm(ops, out_dtype, rows, hidden, eps):
     gen = torch.Generator().manual_seed(2)
     x = torch.randn(rows, hidden, generator=gen) * 3.0
@@ -130,7 +131,8 @@ def test_gemm_tcgen05_exact_on_small_integers(ops, M, N, K):
 
 @pytest.mark.parametrize("M,N,K,bn,splits", [
     (5, 256, 512, 16, 1), (5, 256, 512, 16, 4), (40, 384, 1024, 64, 3), (130, 200, 576, 128, 2),
-    (260, 512, 256, 256, 1), (260, 512, 1024, 256, 2), (70, 130, 176, 32, 1), (24, 3584, 512, 32, 1)])
+    (260, 512, 256, 256, 1), (260, 512, 1024, 256, 2), (70, 130, 176, 32, 1), (24, 3584, 512, 32, 1),
+    (500, 384, 640, 208, 1), (300, 256, 320, 144, 2), (100, 200, 256, 48, 1), (470, 130, 192, 240, 1)])
 def test_gemm_tcgen05_tiles_and_splits(ops, M, N, K, bn, splits):
     gen = torch.Generator().manual_seed(bn + splits + M)
     x = torch.randint(-2, 3, (M, K), generator=gen).to(torch.bfloat16)
@@ -141,7 +143,8 @@ def test_gemm_tcgen05_tiles_and_splits(ops, M, N, K, bn, splits):
     assert torch.equal(out.cpu(), ref)
 
 
-@pytest.mark.parametrize("M,N,K,splits", [(9, 260, 328, 1), (9, 260, 328, 3), (150, 384, 704, 1), (2048, 512, 256, 1)])
+@pytest.mark.parametrize("M,N,K,splits", [(9, 260, 328, 1), (9, 260, 328, 3), (150, 384, 704, 1), (2048, 512, 256, 1),
+                                          (2048, 3584, 128, 1), (1100, 640, 192, 1)])
 def test_gemm_tcgen05_epilogues(ops, M, N, K, splits):
     gen = torch.Generator().manual_seed(7 * M + splits)
     x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
@@ -175,7 +178,8 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_address(ops):
 # rotation + cache store
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(6, 2, 48, 48), (5, 1, 64, 32), (4, 4, 16, 16), (3, 1, 80, 0)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(6, 2, 48, 48), (5, 1, 64, 32), (4, 4, 16, 16), (3, 1, 80, 0),
+                                                          (2, 1, 20, 12), (28, 4, 128, 128), (3, 2, 36, 36)])
 def test_rope_kv_store(ops, dtype, heads, kv_heads, head_dim, rotary):
     from aegean_tge_b200.parts.rope import rotary_tables
     page_size = 16
