@@ -26,7 +26,7 @@ class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, max_model_len: int, use_graphs: bool = True,
                  max_graph_batch: int = 256):
         """``use_graphs``: steps made only of single tokens replay a CUDA graph captured per batch size."""
-        self.use_graphs = use_graphs and not cache.state_specs      # stateful toy mixers loop on the host
+        self.use_graphs = use_graphs and model.graph_safe      # a part that works from host values runs eagerly
         self.max_graph_batch = max_graph_batch
         self._graphs: Dict[tuple, "DecodeGraph"] = {}
         self.graph_replays = 0

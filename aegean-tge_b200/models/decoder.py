@@ -36,6 +36,8 @@ class DecoderModel:
             norm2 = build_part(NORMS, layer.ffn_norm, env)
             self.blocks.append(BLOCKS.get(layer.block)(mixer, ffn, norm1, norm2, env))
         self.layer_caches: List[LayerCache] = [LayerCache() for _ in spec.layers]
+        # single-token steps may be replayed from a CUDA graph only if every part says so
+        self.graph_safe = all(part.graph_safe for _where, part, _spec in self.named_parts())
 
     # -- parameters -----------------------------------------------------------
     def named_parts(self) -> List[Tuple[str, Part, PartSpec]]:

@@ -27,6 +27,7 @@ class GQAttention(Mixer):
     ``position`` (a PartSpec), optional ``scale``.
     weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``.
     """
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -45,6 +46,7 @@ class GQAttention(Mixer):
         self.scale = float(p.get("scale", self.head_dim ** -0.5))
         position: PartSpec = p.get("position", PartSpec("none"))
         self.position = build_part(POSITIONS, position, env)
+        self.graph_safe = bool(self.position.graph_safe)
         self.q_dim = self.heads * self.head_dim
         self.kv_dim = self.kv_heads * self.head_dim
         self.w_qkv: Optional[torch.Tensor] = None

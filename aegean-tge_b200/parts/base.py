@@ -125,6 +125,11 @@ class StepContext:
 # ----------------------------------------------------------------------------
 class Part:
     kind_name = "part"
+    # True when ``forward`` only launches kernels that read the step's device arrays: nothing taken from the
+    # step's host-side values (lengths, slots), no synchronisation, no allocation that depends on the data.
+    # Steps of single tokens are then captured once into a CUDA graph and replayed; one part that leaves
+    # this False makes the whole model run eagerly.
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec

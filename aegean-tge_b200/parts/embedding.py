@@ -17,6 +17,7 @@ from .base import EMBEDDINGS, HEADS, ParamSpec, Part
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
     """params: ``vocab_size``, ``hidden_size``.  weights: ``weight``."""
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -37,6 +38,7 @@ class TokenEmbedding(Part):
 @HEADS.register("linear_head")
 class LinearHead(Part):
     """params: ``vocab_size``, ``hidden_size``.  weights: ``weight`` [vocab, hidden]."""
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

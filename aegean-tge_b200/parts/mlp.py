@@ -18,6 +18,7 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec, StepContext
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
     """params: ``hidden_size``, ``intermediate_size``.  weights: ``gate|up|down.weight``."""
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -17,6 +17,7 @@ from .base import NORMS, Norm, ParamSpec
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """params: ``size`` (row width), ``eps``.  weights: ``weight``."""
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -35,6 +35,7 @@ def rotary_tables(theta: float, rotary: int, positions: int) -> Tuple[torch.Tens
 @POSITIONS.register("rope_neox")
 class RotaryNeoX(PositionEncoding):
     """params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default head_dim)."""
+    graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -56,6 +57,7 @@ class RotaryNeoX(PositionEncoding):
 @POSITIONS.register("none")
 class NoPosition(PositionEncoding):
     """Leaves queries and keys as they are."""
+    graph_safe = True
 
     def rotary_tables(self):
         return None, None, 0
