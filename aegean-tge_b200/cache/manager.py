@@ -16,21 +16,57 @@ context or refuses the load rather than run out (src/models/plan.cpp:72-124).
 Here running out is a run-time event that the scheduler handles; this module
 only answers "does it fit" and moves pages.
 
-All bookkeeping is host-side and needs no GPU; the storage tensors are
-created by ``allocate_storage``.
+All bookkeeping is host-side and needs no GPU.  It is done in C++
+(csrc/runtime.cpp: ``TgeRtCache``); this class maps request ids to the runtime's
+64-bit handles, owns the storage tensors that ``allocate_storage`` creates, and
+forwards everything else.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, Iterator, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
+from .. import runtime as _rt
 from ..parts.base import LayerCache, PagedCacheSpec, StateSpec
 from .pages import PageError, PagePool, PoolExhausted
 
 NO_PAGE = -1
+
+
+class _Tables:
+    """Read-only view of one group's block tables: request -> list of physical page ids."""
+
+    def __init__(self, manager: "CacheManager", group: int):
+        self._manager, self._group = manager, group
+
+    def __getitem__(self, request: Hashable) -> List[int]:
+        m = self._manager
+        if request not in m._handles:
+            raise KeyError(request)
+        handle = m._handles[request]
+        length = _rt.check(m._lib.tge_rt_cache_table_length(m._cache, self._group, handle))
+        out = (ctypes.c_int * max(length, 1))()
+        _rt.check(m._lib.tge_rt_cache_table(m._cache, self._group, handle, out, length))
+        return list(out[:length])
+
+    def __contains__(self, request: Hashable) -> bool:
+        return self._manager.is_live(request)
+
+    def keys(self) -> Tuple[Hashable, ...]:
+        return self._manager.live_requests()
+
+    def values(self) -> Iterator[List[int]]:
+        return (self[request] for request in self.keys())
+
+    def items(self) -> Iterator[Tuple[Hashable, List[int]]]:
+        return ((request, self[request]) for request in self.keys())
+
+    def __len__(self) -> int:
+        return len(self.keys())
 
 
 @dataclass
@@ -39,7 +75,7 @@ class PageGroup:
     layers: List[int]
     page_size: int
     pool: PagePool
-    tables: Dict[Hashable, List[int]] = field(default_factory=dict)    # request -> logical page -> physical id
+    tables: _Tables
     storage: Dict[str, torch.Tensor] = field(default_factory=dict)      # name -> [layers, pages, ...]
 
     def bytes_per_page(self, element_size: int) -> int:
@@ -65,15 +101,56 @@ class CacheManager:
             raise ValueError("cache manager: page_size and max_requests must be positive")
         self.page_size = page_size
         self.max_requests = max_requests
+        self._lib = _rt.lib()
+        self._cache = self._lib.tge_rt_cache_create(int(page_size), int(max_requests))
         self.groups: List[PageGroup] = []
         self.layer_group: Dict[int, int] = {}                # layer id -> group index
         self.layer_row: Dict[int, int] = {}                  # layer id -> row in the group's storage
         self.state_specs: Dict[int, StateSpec] = {}          # layer id -> its state
         self.state_storage: Dict[int, Dict[str, torch.Tensor]] = {}
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        self._slot_of: Dict[Hashable, int] = {}
-        self._tokens: Dict[Hashable, int] = {}               # request -> tokens its pages cover
-        self._computed: Dict[Hashable, int] = {}             # request -> tokens whose entries are written
+        # request id <-> the runtime's handle; a mapping lives while the request is live here or pinned
+        # by the scheduler
+        self._handles: Dict[Hashable, int] = {}
+        self._names: Dict[int, Hashable] = {}
+        self._pinned: set = set()
+        self._next_handle = 1
+
+    def __del__(self):
+        if getattr(self, "_cache", None):
+            self._lib.tge_rt_cache_destroy(self._cache)
+            self._cache = None
+
+    # -- request ids ------------------------------------------------------------
+    def handle_of(self, request: Hashable, create: bool = False) -> int:
+        handle = self._handles.get(request)
+        if handle is None:
+            if not create:
+                raise PageError(f"cache manager: request {request!r} is not live")
+            handle = self._next_handle
+            self._next_handle += 1
+            self._handles[request] = handle
+            self._names[handle] = request
+        return handle
+
+    def name_of(self, handle: int) -> Hashable:
+        return self._names[handle]
+
+    def pin(self, request: Hashable) -> int:
+        """Keeps the request's handle although it holds nothing here (the scheduler's waiting queue)."""
+        handle = self.handle_of(request, create=True)
+        self._pinned.add(request)
+        return handle
+
+    def unpin(self, request: Hashable) -> None:
+        self._pinned.discard(request)
+        self._drop_handle(request)
+
+    def _drop_handle(self, request: Hashable) -> None:
+        if request in self._pinned or request not in self._handles:
+            return
+        if self._lib.tge_rt_cache_is_live(self._cache, self._handles[request]):
+            return
+        self._names.pop(self._handles.pop(request), None)
 
     # -- construction ---------------------------------------------------------
     def add_layer(self, layer: int, cache: Optional[PagedCacheSpec], state: Optional[StateSpec]) -> None:
@@ -86,19 +163,23 @@ class CacheManager:
                     group.layers.append(layer)
                     break
             else:
-                self.layer_group[layer] = len(self.groups)
+                index = _rt.check(self._lib.tge_rt_cache_add_group(self._cache, -1 if cache.window is None else int(cache.window)))
+                assert index == len(self.groups)
+                self.layer_group[layer] = index
                 self.layer_row[layer] = 0
-                self.groups.append(PageGroup(cache, [layer], self.page_size, PagePool(1)))
+                pool = PagePool(_borrowed=self._lib.tge_rt_cache_pool(self._cache, index))
+                self.groups.append(PageGroup(cache, [layer], self.page_size, pool, _Tables(self, index)))
         if state is not None:
             self.state_specs[layer] = state
 
     def set_pool_sizes(self, pages_per_group: Sequence[int]) -> None:
         if len(pages_per_group) != len(self.groups):
             raise ValueError("cache manager: one page count per group")
-        if self._slot_of:
+        if self._lib.tge_rt_cache_live_count(self._cache):
             raise RuntimeError("cache manager: pools cannot be resized while requests are live")
-        for group, count in zip(self.groups, pages_per_group):
-            group.pool = PagePool(int(count))
+        for index, (group, count) in enumerate(zip(self.groups, pages_per_group)):
+            _rt.check(self._lib.tge_rt_cache_set_pool_size(self._cache, index, int(count)))
+            group.pool = PagePool(_borrowed=self._lib.tge_rt_cache_pool(self._cache, index))
 
     def plan_pool_sizes(self, *, tokens: Optional[int] = None, budget_bytes: Optional[int] = None,
                         element_size: int = 2) -> List[int]:
@@ -156,62 +237,70 @@ class CacheManager:
 
     # -- requests -------------------------------------------------------------
     @property
+    def native(self):
+        """The runtime's cache object (for the scheduler and the step packer)."""
+        return self._cache
+
+    @property
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.tge_rt_cache_free_slots(self._cache)
 
     def live_requests(self) -> Tuple[Hashable, ...]:
-        return tuple(self._slot_of)
+        count = self._lib.tge_rt_cache_live_count(self._cache)
+        out = (ctypes.c_int64 * max(count, 1))()
+        self._lib.tge_rt_cache_live_requests(self._cache, out, count)
+        return tuple(self._names[h] for h in out[:count])
 
     def slot_of(self, request: Hashable) -> int:
-        return self._slot_of[request]
+        return _rt.check(self._lib.tge_rt_cache_slot_of(self._cache, self._live_handle(request)))
 
     def tokens_of(self, request: Hashable) -> int:
-        return self._tokens[request]
+        return _rt.check(self._lib.tge_rt_cache_tokens_of(self._cache, self._live_handle(request)))
 
     def is_live(self, request: Hashable) -> bool:
-        return request in self._slot_of
+        handle = self._handles.get(request)
+        return handle is not None and bool(self._lib.tge_rt_cache_is_live(self._cache, handle))
+
+    def _live_handle(self, request: Hashable) -> int:
+        handle = self._handles.get(request)
+        if handle is None:
+            raise KeyError(request)
+        return handle
 
     def computed(self, request: Hashable) -> int:
         """Tokens of the request whose cache entries have been written by finished steps."""
-        return self._computed[request]
+        return _rt.check(self._lib.tge_rt_cache_computed(self._cache, self._live_handle(request)))
 
     def set_computed(self, request: Hashable, tokens: int) -> None:
         """Records progress (never backwards) and gives back pages a window has passed."""
-        if tokens > self._tokens[request]:
-            raise PageError(f"cache manager: request {request!r} computed {tokens} tokens but holds pages for "
-                            f"{self._tokens[request]}")
-        if tokens > self._computed[request]:
-            self._computed[request] = tokens
-        self.release_behind_window(request, self._computed[request])
+        _rt.check(self._lib.tge_rt_cache_set_computed(self._cache, self.handle_of(request), int(tokens)))
 
     def admit(self, request: Hashable) -> int:
         """Gives the request a state slot (zeroed) and empty block tables."""
-        if request in self._slot_of:
-            raise PageError(f"cache manager: request {request!r} is already live")
-        if not self._free_slots:
-            raise PoolExhausted("cache manager: no free state slot")
-        slot = self._free_slots.pop()
-        self._slot_of[request] = slot
-        self._tokens[request] = 0
-        self._computed[request] = 0
-        for group in self.groups:
-            group.tables[request] = []
+        fresh = request not in self._handles
+        try:
+            slot = _rt.check(self._lib.tge_rt_cache_admit(self._cache, self.handle_of(request, create=True)))
+        except Exception:
+            if fresh:
+                self._drop_handle(request)
+            raise
+        self.zero_state(slot)
+        return slot
+
+    def zero_state(self, slot: int) -> None:
         for tensors in self.state_storage.values():
             for tensor in tensors.values():
                 tensor[slot].zero_()
-        return slot
 
     def pages_missing(self, request: Hashable, total_tokens: int, computed_tokens: Optional[int] = None) -> List[int]:
         """Per group, pages that must be allocated so the request covers ``total_tokens`` positions."""
-        missing = []
-        need = -(-total_tokens // self.page_size)
-        for group in self.groups:
-            have = len(group.tables[request]) if request in group.tables else 0
-            missing.append(max(need - have, 0))
-        return missing
+        out = (ctypes.c_int * 8)()
+        handle = self._handles.get(request, 0)
+        count = self._lib.tge_rt_cache_pages_missing(self._cache, handle, int(total_tokens), out)
+        return list(out[:count])
 
     def can_grow(self, request: Hashable, total_tokens: int) -> bool:
-        return all(m <= g.pool.free_count for m, g in zip(self.pages_missing(request, total_tokens), self.groups))
+        return bool(self._lib.tge_rt_cache_can_grow(self._cache, self._handles.get(request, 0), int(total_tokens)))
 
     def fits_empty_pool(self, total_tokens: int) -> bool:
         """Whether a request of this many tokens could ever fit, alone, in every pool.
@@ -219,80 +308,42 @@ class CacheManager:
         A windowed group holds at most the pages its window spans plus the
         pages a step's portion adds, which never exceeds the full count.
         """
-        need = -(-total_tokens // self.page_size)
-        return all(need <= g.pool.capacity for g in self.groups)
+        return bool(self._lib.tge_rt_cache_fits_empty_pool(self._cache, int(total_tokens)))
 
     def grow(self, request: Hashable, total_tokens: int) -> None:
         """Allocates pages so that positions [0, total_tokens) are covered.  All or nothing."""
-        if request not in self._slot_of:
-            raise PageError(f"cache manager: request {request!r} is not live")
-        missing = self.pages_missing(request, total_tokens)
-        for m, group in zip(missing, self.groups):
-            if m > group.pool.free_count:
-                raise PoolExhausted(f"cache manager: request {request!r} needs {m} more pages, "
-                                    f"{group.pool.free_count} are free")
-        for m, group in zip(missing, self.groups):
-            table = group.tables[request]
-            for _ in range(m):
-                table.append(group.pool.allocate())
-        self._tokens[request] = max(self._tokens[request], total_tokens)
+        _rt.check(self._lib.tge_rt_cache_grow(self._cache, self.handle_of(request), int(total_tokens)))
 
     def release_behind_window(self, request: Hashable, computed_tokens: int) -> int:
         """Gives back pages that no query at position >= computed_tokens can read.  Returns how many."""
-        released = 0
-        for group in self.groups:
-            table = group.tables[request]
-            for index in range(min(group.first_needed_page(computed_tokens), len(table))):
-                if table[index] != NO_PAGE:
-                    group.pool.release(table[index])
-                    table[index] = NO_PAGE
-                    released += 1
-        return released
+        return _rt.check(self._lib.tge_rt_cache_release_behind_window(self._cache, self.handle_of(request),
+                                                                      int(computed_tokens)))
 
     def free(self, request: Hashable) -> None:
         """Gives back everything the request holds."""
-        if request not in self._slot_of:
+        if request not in self._handles:
             raise PageError(f"cache manager: request {request!r} is not live (freed twice?)")
-        for group in self.groups:
-            for page in group.tables.pop(request):
-                if page != NO_PAGE:
-                    group.pool.release(page)
-        self._free_slots.append(self._slot_of.pop(request))
-        del self._tokens[request]
-        del self._computed[request]
+        _rt.check(self._lib.tge_rt_cache_free(self._cache, self._handles[request]))
+        self._drop_handle(request)
+
+    def forget_dead_handles(self) -> None:
+        """Drops id mappings of requests the runtime freed on its own (the scheduler finishing a request)."""
+        for request in [r for r in self._handles if r not in self._pinned]:
+            self._drop_handle(request)
 
     def fill_block_table(self, group_index: int, requests: Sequence[Hashable], out: "np.ndarray") -> None:
         """Writes the requests' page ids into ``out`` (int32 [len(requests), width]), NO_PAGE beyond each row's end."""
-        group = self.groups[group_index]
-        out.fill(NO_PAGE)
-        for row, request in enumerate(requests):
-            table = group.tables[request]
-            out[row, :len(table)] = table
+        handles = (ctypes.c_int64 * len(requests))(*[self.handle_of(r) for r in requests])
+        assert out.dtype == np.int32 and out.flags["C_CONTIGUOUS"]
+        _rt.check(self._lib.tge_rt_cache_fill_block_table(self._cache, group_index, handles, len(requests),
+                                                          out.ctypes.data, out.shape[1]))
 
     def block_table(self, group_index: int, requests: Sequence[Hashable], width: Optional[int] = None) -> List[List[int]]:
         """Rows of physical page ids, padded with NO_PAGE to a common width."""
-        group = self.groups[group_index]
-        rows = [group.tables[r] for r in requests]
+        rows = [self.groups[group_index].tables[r] for r in requests]
         width = max([len(r) for r in rows] + [1]) if width is None else width
         return [row + [NO_PAGE] * (width - len(row)) for row in rows]
 
     def check(self) -> None:
         """No page lost, held twice, or free while referenced; slots consistent."""
-        for group in self.groups:
-            group.pool.check()
-            held: Dict[int, int] = {}
-            for request, table in group.tables.items():
-                if request not in self._slot_of:
-                    raise PageError(f"cache manager: a table exists for dead request {request!r}")
-                for page in table:
-                    if page != NO_PAGE:
-                        held[page] = held.get(page, 0) + 1
-            for page in range(group.pool.capacity):
-                if group.pool.refcount(page) != held.get(page, 0):
-                    raise PageError(f"cache manager: page {page} is held {held.get(page, 0)} times "
-                                    f"but counts {group.pool.refcount(page)} references")
-        slots = list(self._slot_of.values())
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
-            raise PageError("cache manager: a state slot is held twice")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise PageError("cache manager: a state slot is lost")
+        _rt.check(self._lib.tge_rt_cache_check(self._cache))

@@ -1,9 +1,11 @@
-"""Compiles the CUDA sources in this folder into shared libraries, in-tree.
+"""Compiles the sources in this folder into shared libraries, in-tree.
 
-Two kinds of library exist:
+Three kinds of library exist:
 
-* ``libtge_core.so`` - everything that does not depend on the model;
-* ``libtge_attn_hd<N>.so`` - the tensor-core attention kernel for one head
+* ``libtge_runtime.so`` - the host runtime (page pools, cache bookkeeping,
+  scheduler, step packing): plain C++, needs no CUDA;
+* ``libtge_core.so`` - every kernel that does not depend on the model;
+* ``libtge_attn_hd<N>.so`` - the tensor-core attention kernels for one head
   size, compiled when a model with that head size is first built.
 
 A library is rebuilt when the hash of its sources and flags changes.  Builds
@@ -30,6 +32,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcomp
 CORE_SOURCES = ["host_util.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu", "sampling.cu", "sampling_cuts.cu",
                 "gemm_static_scratch.cu"]
 HEADERS = ["common.cuh", "gemm_static_scratch.h", "attention_tc.cuh"]
+RUNTIME_SOURCES = ["runtime.cpp"]
+RUNTIME_HEADERS = ["runtime.h"]
 
 
 class BuildError(RuntimeError):
@@ -67,9 +71,18 @@ def build_dir() -> str:
         return fallback
 
 
-def _hash(sources: Sequence[str], flags: Sequence[str]) -> str:
+def find_host_compiler() -> List[str]:
+    """The C++ compiler for the host runtime: g++ or c++ if there is one, else nvcc (which calls one)."""
+    for name in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(name) if name else None
+        if path:
+            return [path]
+    return [find_nvcc(), "-x", "c++"]
+
+
+def _hash(sources: Sequence[str], flags: Sequence[str], headers: Sequence[str] = ()) -> str:
     digest = hashlib.sha256()
-    for name in list(sources) + HEADERS:
+    for name in list(sources) + list(headers or HEADERS):
         path = os.path.join(CSRC, name)
         digest.update(name.encode())
         with open(path, "rb") as handle:
@@ -134,6 +147,48 @@ def _build(lib_name: str, sources: Sequence[str], flags: Sequence[str]) -> str:
     return lib_path
 
 
+def build_runtime() -> str:
+    """The host runtime, one translation unit, compiled with the host compiler."""
+    out_dir = build_dir()
+    lib_path = os.path.join(out_dir, "libtge_runtime.so")
+    stamp_path = lib_path + ".hash"
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared"]
+    wanted = _hash(RUNTIME_SOURCES, flags, RUNTIME_HEADERS)
+
+    def fresh() -> bool:
+        if not os.path.isfile(lib_path) or not os.path.isfile(stamp_path):
+            return False
+        with open(stamp_path, "r") as handle:
+            return handle.read().strip() == wanted
+
+    if fresh():
+        return lib_path
+    with open(lib_path + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if fresh():
+                return lib_path
+            compiler = find_host_compiler()
+            started = time.time()
+            _log(f"building libtge_runtime.so with {compiler[0]}")
+            tmp_path = lib_path + f".tmp{os.getpid()}"
+            if os.path.basename(compiler[0]).startswith("nvcc"):
+                cmd = [*compiler, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+            else:
+                cmd = [*compiler, *flags]
+            cmd += [os.path.join(CSRC, name) for name in RUNTIME_SOURCES] + ["-o", tmp_path]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise BuildError(f"compiling the host runtime failed:\n{proc.stdout}\n{proc.stderr}")
+            os.replace(tmp_path, lib_path)
+            with open(stamp_path, "w") as handle:
+                handle.write(wanted)
+            _log(f"built libtge_runtime.so in {time.time() - started:.1f} s")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return lib_path
+
+
 def build_core() -> str:
     return _build("libtge_core.so", CORE_SOURCES, [])
 
@@ -147,7 +202,7 @@ def build_attention(head_dim: int) -> str:
 
 
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
-    paths = [build_core()]
+    paths = [build_runtime(), build_core()]
     for head_dim in head_dims:
         paths.append(build_attention(head_dim))
     return paths

@@ -6,14 +6,23 @@ places among them whose logits are wanted.  The reference's nearest notion is
 the row list ``(token, position, sequence)`` of ``forward_batch``
 (src/models/qwen2.cpp:1613-1639); positions are not given here because the
 cache knows how many tokens a request already holds.
+
+The index arrays of a step (token ids, positions, portion of each token,
+portion starts, start positions, context lengths, state slots, wanted rows,
+one block table per cache group) are packed by the host runtime
+(csrc/runtime.cpp: ``pack_step``) into one int32 buffer in pinned memory, which
+is copied to the device once.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
-from typing import Hashable, List, Sequence
+from typing import Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
+from .. import runtime as _rt
 from ..parts.base import StepContext
 
 
@@ -34,61 +43,44 @@ class Portion:
                 raise ValueError(f"request {self.request!r}: wanted place {place} is outside its {len(self.tokens)} tokens")
 
 
-def build_context(portions: Sequence[Portion], start_positions: Sequence[int], slots: Sequence[int],
-                  block_tables: Sequence[Sequence[Sequence[int]]], device: torch.device):
-    """Packs the step's index arrays into one pinned buffer, copies it once, and slices it.
+def _int32(values: Sequence[int], what: str, request: Hashable) -> np.ndarray:
+    try:
+        return np.ascontiguousarray(values, dtype=np.int32)
+    except (OverflowError, ValueError, TypeError) as error:
+        raise ValueError(f"request {request!r}: {what} are not 32-bit integers ({error})") from None
 
-    Returns (StepContext, logit_rows tensor or None).
-    """
-    num_seqs = len(portions)
-    lengths = [len(p.tokens) for p in portions]
-    total = sum(lengths)
-    token_ids: List[int] = []
-    positions: List[int] = []
-    seq_of_token: List[int] = []
-    q_start = [0]
-    logit_rows: List[int] = []
-    for index, (portion, start) in enumerate(zip(portions, start_positions)):
-        base = q_start[-1]
-        token_ids.extend(int(t) for t in portion.tokens)
-        positions.extend(range(start, start + lengths[index]))
-        seq_of_token.extend([index] * lengths[index])
-        logit_rows.extend(base + int(w) for w in portion.want)
-        q_start.append(base + lengths[index])
-    ctx_len = [s + n for s, n in zip(start_positions, lengths)]
-    widths = [len(table[0]) if table else 1 for table in block_tables]
-    flat: List[int] = []
-    offsets = {}
 
-    def put(name: str, values: Sequence[int]) -> None:
-        offsets[name] = (len(flat), len(values))
-        flat.extend(values)
+class PortionArrays:
+    """The portions of one step as the arrays the runtime's packer reads."""
 
-    put("token_ids", token_ids)
-    put("positions", positions)
-    put("seq_of_token", seq_of_token)
-    put("q_start", q_start)
-    put("start_pos", list(start_positions))
-    put("ctx_len", ctx_len)
-    put("slots", list(slots))
-    put("logit_rows", logit_rows)
-    for g, table in enumerate(block_tables):
-        put(f"table{g}", [page for row in table for page in row])
-    host = torch.tensor(flat, dtype=torch.int32)
-    if device.type == "cuda":
-        host = host.pin_memory()
-    dev = host.to(device, non_blocking=True)
+    def __init__(self, cache, portions: Sequence[Portion]):
+        count = len(portions)
+        self.count = count
+        self.requests = [p.request for p in portions]
+        self.tokens = [_int32(p.tokens, "tokens", p.request) for p in portions]
+        self.wants = [_int32(p.want, "wanted places", p.request) for p in portions]
+        self.handles = (ctypes.c_int64 * count)(*[cache.handle_of(r, create=True) for r in self.requests])
+        self.token_ptrs = (ctypes.c_void_p * count)(*[t.ctypes.data for t in self.tokens])
+        self.token_counts = (ctypes.c_int * count)(*[t.size for t in self.tokens])
+        self.want_ptrs = (ctypes.c_void_p * count)(*[w.ctypes.data for w in self.wants])
+        self.want_counts = (ctypes.c_int * count)(*[w.size for w in self.wants])
+        self.single_tokens = all(t.size == 1 for t in self.tokens)
 
-    def take(name: str) -> torch.Tensor:
-        begin, count = offsets[name]
-        return dev[begin:begin + count]
 
+def context_from_packed(dev: torch.Tensor, host: np.ndarray, layout: "_rt.StepLayout", groups: int,
+                        max_ctx_len: Optional[int] = None, typical_ctx_len: int = 0) -> Tuple[StepContext, Optional[torch.Tensor]]:
+    """Slices the packed device buffer into a :class:`StepContext`; host lists come from the host copy."""
+    L = layout
+    T, S, R = L.num_tokens, L.num_seqs, L.num_rows
+    take = lambda begin, count: dev[begin:begin + count]
+    q_start = host[L.q_start:L.q_start + S + 1]
     ctx = StepContext(
-        num_tokens=total, num_seqs=num_seqs, token_ids=take("token_ids"), positions=take("positions"),
-        seq_of_token=take("seq_of_token"), q_start=take("q_start"), start_pos=take("start_pos"),
-        ctx_len=take("ctx_len"), slots=take("slots"),
-        block_tables=[take(f"table{g}").view(num_seqs, widths[g]) for g in range(len(block_tables))],
-        max_q_len=max(lengths), max_ctx_len=max(ctx_len), host_q_lens=lengths,
-        host_start_pos=list(start_positions), host_slots=list(slots))
-    rows = take("logit_rows") if logit_rows else None
-    return ctx, rows, host.numel() * 4
+        num_tokens=T, num_seqs=S, token_ids=take(L.token_ids, T), positions=take(L.positions, T),
+        seq_of_token=take(L.seq_of_token, T), q_start=take(L.q_start, S + 1), start_pos=take(L.start_pos, S),
+        ctx_len=take(L.ctx_len, S), slots=take(L.slots, S),
+        block_tables=[take(L.table[g], S * L.width[g]).view(S, L.width[g]) for g in range(groups)],
+        max_q_len=L.max_q_len, max_ctx_len=L.max_ctx_len if max_ctx_len is None else max_ctx_len,
+        typical_ctx_len=typical_ctx_len, host_q_lens=np.diff(q_start).tolist(),
+        host_start_pos=host[L.start_pos:L.start_pos + S].tolist(), host_slots=host[L.slots:L.slots + S].tolist())
+    rows = take(L.logit_rows, R) if R else None
+    return ctx, rows

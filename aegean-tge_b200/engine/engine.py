@@ -125,7 +125,7 @@ class Engine:
     def step(self) -> List[Request]:
         """Plans one step, runs it, samples, and returns the requests that finished in it."""
         plan = self.scheduler.schedule()
-        logits = self.runner.step(plan.portions())
+        logits = self.runner.step_plan(plan)
         sampling_items = [item for item in plan.items if item.samples]
         sampled: List[int] = []
         if sampling_items:

@@ -12,14 +12,50 @@ one weight pass.
 """
 from __future__ import annotations
 
-from typing import Dict, Hashable, List, Optional, Sequence
+import ctypes
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
+from .. import runtime as _rt
 from ..cache.manager import CacheManager
 from ..cache.pages import PoolExhausted
 from ..models.decoder import DecoderModel
-from .batch import Portion, build_context
+from .batch import Portion, PortionArrays, context_from_packed
+
+# packs the step's index arrays: (fixed table width or 0, rows to pad to or 0, int32 buffer, layout) -> ints used
+Packer = Callable[[int, int, np.ndarray, "_rt.StepLayout"], int]
+
+
+class Staging:
+    """A ring of pinned host buffers.  The host fills the next one while earlier copies are still queued;
+    a buffer is used again only after the copy that read it has finished."""
+
+    def __init__(self, ints: int, ring: int = 4):
+        self.ring = ring
+        self.hosts = [torch.zeros(ints, dtype=torch.int32).pin_memory() for _ in range(ring)]
+        self.views = [host.numpy() for host in self.hosts]
+        self.copied: List[Optional[torch.cuda.Event]] = [None] * ring
+        self.turn = 0
+
+    def take(self, ints: int = 0) -> int:
+        """The next buffer's index, free to be written, at least ``ints`` long."""
+        turn = self.turn
+        self.turn = (turn + 1) % self.ring
+        if self.copied[turn] is not None:
+            self.copied[turn].synchronize()
+            self.copied[turn] = None
+        if self.hosts[turn].numel() < ints:
+            self.hosts[turn] = torch.zeros(max(ints, 2 * self.hosts[turn].numel()), dtype=torch.int32).pin_memory()
+            self.views[turn] = self.hosts[turn].numpy()
+        return turn
+
+    def queued(self, turn: int) -> None:
+        """Call after the copy out of buffer ``turn`` was queued on the current stream."""
+        event = torch.cuda.Event()
+        event.record()
+        self.copied[turn] = event
 
 
 class ModelRunner:
@@ -38,6 +74,9 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.h2d_bytes_last = 0
+        self._lib = _rt.lib()
+        self._staging: Optional[Staging] = None
+        self._widest = -(-max_model_len // cache.page_size)
 
     # -- request lifetime -----------------------------------------------------
     def is_live(self, request: Hashable) -> bool:
@@ -55,63 +94,87 @@ class ModelRunner:
         """Runs one batch.  Returns float32 logits [wanted rows, vocab] on the device, or None."""
         if not portions:
             return None
-        seen = set()
+        cache, lib = self.cache, self._lib
+        arrays = PortionArrays(cache, portions)
+        fresh = [r for r in arrays.requests if not cache.is_live(r)] if cache.state_storage else []
         vocab = self.model.spec.vocab_size
-        for portion in portions:
-            if portion.request in seen:
-                raise ValueError(f"request {portion.request!r} appears twice in one step")
-            seen.add(portion.request)
-            portion.validate(vocab)
-        # reserve everything before touching anything, so a step either runs whole or not at all
-        # (a request the scheduler already admitted and grew is left as it is: both calls are idempotent)
-        admitted: List[Hashable] = []
+
+        def pack(width: int, pad_rows: int, out: np.ndarray, layout) -> int:
+            # admits unknown requests and grows pages, all or nothing, then writes the arrays
+            return _rt.check(lib.tge_rt_step_pack(cache.native, arrays.count, arrays.handles, arrays.token_ptrs,
+                                                  arrays.token_counts, arrays.want_ptrs, arrays.want_counts, vocab,
+                                                  self.max_model_len, width, pad_rows, out.ctypes.data, out.size,
+                                                  ctypes.byref(layout)))
+
+        def packed() -> None:
+            for request in fresh:                 # a request that starts gets a zeroed state slot
+                cache.zero_state(cache.slot_of(request))
+
+        max_ctx = lib.tge_rt_cache_max_context(cache.native, arrays.handles, arrays.token_counts, arrays.count)
+        tokens = int(sum(arrays.token_counts))
+        wanted = [i for i, w in enumerate(arrays.wants) if w.size]
         try:
-            for portion in portions:
-                if not self.cache.is_live(portion.request):
-                    self.cache.admit(portion.request)
-                    admitted.append(portion.request)
-                total = self.cache.computed(portion.request) + len(portion.tokens)
-                if total > self.max_model_len:
-                    raise ValueError(f"request {portion.request!r}: {total} tokens exceed the context of {self.max_model_len}")
-                self.cache.grow(portion.request, total)
+            logits = self._run(pack, arrays.count, tokens, arrays.single_tokens, max_ctx, wanted, packed)
         except (PoolExhausted, ValueError):
-            for request in admitted:
-                self.cache.free(request)
+            cache.forget_dead_handles()
             raise
-        requests = [p.request for p in portions]
-        starts = [self.cache.computed(r) for r in requests]
-        slots = [self.cache.slot_of(r) for r in requests]
-        batch = len(portions)
-        if self.use_graphs and batch <= self.max_graph_batch and all(len(p.tokens) == 1 for p in portions):
+        _rt.check(lib.tge_rt_cache_advance(cache.native, arrays.handles, arrays.token_counts, arrays.count))
+        return logits
+
+    def step_plan(self, plan) -> Optional[torch.Tensor]:
+        """Runs a scheduler's plan: the same step, packed from the scheduler's own copies of the tokens.
+
+        Pages were reserved when the plan was made, and the scheduler records progress in ``update``.
+        """
+        items = plan.items
+        if not items:
+            return None
+        vocab = self.model.spec.vocab_size
+        single = all(item.count == 1 for item in items)
+        max_ctx = max(item.start + item.count for item in items)
+        tokens = sum(item.count for item in items)
+        wanted = [i for i, item in enumerate(items) if item.samples]
+        return self._run(lambda width, pad_rows, out, layout: plan.pack(vocab, width, pad_rows, out, layout),
+                         len(items), tokens, single, max_ctx, wanted, None)
+
+    def _run(self, pack: Packer, batch: int, tokens: int, single: bool, max_ctx: int, wanted: List[int],
+             packed: Optional[Callable[[], None]]) -> Optional[torch.Tensor]:
+        groups = len(self.cache.groups)
+        if self.use_graphs and single and batch <= self.max_graph_batch:
             bound = 1024
-            while bound < max(starts) + 1:
+            while bound < max_ctx:
                 bound *= 2
             bound = min(bound, self.max_model_len)
             graph = self._graphs.get((batch, bound))
             if graph is None:
                 graph = self._graphs[(batch, bound)] = DecodeGraph(self, batch, bound)
-            logits = graph.run(self.cache, requests, [int(p.tokens[0]) for p in portions], starts, slots)
+            logits = graph.run(pack, packed)
             self.ops.launches += graph.kernels
             self.h2d_bytes_last = graph.nbytes
             self.graph_replays += 1
-            wanted = [i for i, p in enumerate(portions) if len(p.want)]
             if not wanted:
                 logits = None
             elif len(wanted) != batch:
                 logits = logits[torch.tensor(wanted, device=self.device)]
             else:
                 logits = logits.clone()          # the graph's own buffer is overwritten by the next replay
-            num_tokens = batch
         else:
-            tables = [self.cache.block_table(g, requests) for g in range(len(self.cache.groups))]
-            ctx, rows, h2d = build_context(portions, starts, slots, tables, self.device)
-            self.h2d_bytes_last = h2d
+            need = 4 * tokens + 4 * batch + 1 + groups * batch * self._widest
+            if self._staging is None:
+                self._staging = Staging(max(need, 1 << 14))
+            staging = self._staging
+            turn = staging.take(need)
+            layout = _rt.StepLayout()
+            total = pack(0, 0, staging.views[turn], layout)
+            if packed is not None:
+                packed()
+            dev = staging.hosts[turn][:total].to(self.device, non_blocking=True)
+            staging.queued(turn)
+            self.h2d_bytes_last = total * 4
+            ctx, rows = context_from_packed(dev, staging.views[turn], layout, groups)
             logits = self.model.forward(ctx, rows)
-            num_tokens = ctx.num_tokens
-        for portion, start in zip(portions, starts):
-            self.cache.set_computed(portion.request, start + len(portion.tokens))
         self.steps += 1
-        self.tokens_run += num_tokens
+        self.tokens_run += tokens
         return logits
 
 
@@ -125,49 +188,39 @@ class DecodeGraph:
     """
 
     def __init__(self, runner: "ModelRunner", batch: int, max_ctx: int):
-        from ..parts.base import StepContext
         self.batch = batch
         self.max_ctx = max_ctx
         model, cache = runner.model, runner.cache
         device = runner.device
         self.width = -(-max_ctx // cache.page_size)
         groups = len(cache.groups)
-        sizes = [("token_ids", batch), ("positions", batch), ("seq_of_token", batch), ("q_start", batch + 1),
-                 ("start_pos", batch), ("ctx_len", batch), ("slots", batch), ("rows", batch)]
-        sizes += [(f"table{g}", batch * self.width) for g in range(groups)]
-        self.offsets, cursor = {}, 0
-        for name, count in sizes:
-            self.offsets[name] = (cursor, count)
+        # the packer's layout for `batch` single tokens, tables `width` wide, rows padded to `batch`
+        L = self.layout = _rt.StepLayout()
+        cursor = 0
+        for name, count in (("token_ids", batch), ("positions", batch), ("seq_of_token", batch), ("q_start", batch + 1),
+                            ("start_pos", batch), ("ctx_len", batch), ("slots", batch), ("logit_rows", batch)):
+            setattr(L, name, cursor)
             cursor += count
-        # A ring of pinned staging buffers: the host may fill the next one while earlier copies are
-        # still queued; a buffer is reused only after the copy that read it has finished.
-        self.ring = 4
-        self.hosts = [torch.zeros(cursor, dtype=torch.int32).pin_memory() for _ in range(self.ring)]
-        self.copied = [None] * self.ring
-        self.turn = 0
+        for g in range(groups):
+            L.table[g], L.width[g] = cursor, self.width
+            cursor += batch * self.width
+        L.num_tokens = L.num_seqs = L.num_rows = batch
+        L.max_q_len, L.max_ctx_len, L.total_ints = 1, max_ctx, cursor
+        self.staging = Staging(cursor)
         self.dev = torch.zeros(cursor, dtype=torch.int32, device=device)
-        view = lambda t, name: t[self.offsets[name][0]:self.offsets[name][0] + self.offsets[name][1]]
-        self.hs = [{name: view(host, name) for name, _ in sizes} for host in self.hosts]
-        self.np_hs = [{name: tensor.numpy() for name, tensor in h.items()} for h in self.hs]   # same memory, cheap to fill
-        d = {name: view(self.dev, name) for name, _ in sizes}
-        for h in self.hs:
-            # constants of a decode step
-            h["seq_of_token"].copy_(torch.arange(batch, dtype=torch.int32))
-            h["q_start"].copy_(torch.arange(batch + 1, dtype=torch.int32))
-            h["rows"].copy_(torch.arange(batch, dtype=torch.int32))
-            # warm-up contents: every request one token at position 0 on the scratch page
-            h["ctx_len"].fill_(1)
-            for g, group in enumerate(cache.groups):
-                h[f"table{g}"].fill_(group.pool.capacity)
-        self.dev.copy_(self.hosts[0])
+        # warm-up contents: every request one token at position 0 on the scratch page
+        warm = self.staging.views[0]
+        warm[L.seq_of_token:L.seq_of_token + batch] = np.arange(batch)
+        warm[L.q_start:L.q_start + batch + 1] = np.arange(batch + 1)
+        warm[L.logit_rows:L.logit_rows + batch] = np.arange(batch)
+        warm[L.ctx_len:L.ctx_len + batch] = 1
+        for g, group in enumerate(cache.groups):
+            warm[L.table[g]:L.table[g] + batch * self.width] = group.pool.capacity
+        self.dev.copy_(self.staging.hosts[0])
         self.nbytes = cursor * 4
-        self.ctx = StepContext(
-            num_tokens=batch, num_seqs=batch, token_ids=d["token_ids"], positions=d["positions"],
-            seq_of_token=d["seq_of_token"], q_start=d["q_start"], start_pos=d["start_pos"], ctx_len=d["ctx_len"],
-            slots=d["slots"], block_tables=[d[f"table{g}"].view(batch, self.width) for g in range(groups)],
-            max_q_len=1, max_ctx_len=max_ctx, typical_ctx_len=max_ctx // 2 + 1, host_q_lens=[1] * batch, host_start_pos=[0] * batch,
-            host_slots=[0] * batch)
-        self.rows = d["rows"]
+        self.ctx, _ = context_from_packed(self.dev, warm, L, groups, max_ctx_len=max_ctx, typical_ctx_len=max_ctx // 2 + 1)
+        # all rows' logits are computed; the rows a step wants are picked afterwards
+        self.rows = torch.arange(batch, dtype=torch.int32, device=device)
         ops = runner.ops
         side = torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
@@ -183,23 +236,16 @@ class DecodeGraph:
         self.kernels = ops.launches - before
         ops.launches = before
 
-    def run(self, cache: CacheManager, requests, tokens, positions, slots) -> torch.Tensor:
-        turn = self.turn
-        self.turn = (turn + 1) % self.ring
-        if self.copied[turn] is not None:
-            self.copied[turn].synchronize()
-        h = self.np_hs[turn]
-        h["token_ids"][:] = tokens
-        h["positions"][:] = positions
-        h["start_pos"][:] = positions
-        h["ctx_len"][:] = positions
-        h["ctx_len"] += 1
-        h["slots"][:] = slots
-        for g in range(len(cache.groups)):
-            cache.fill_block_table(g, requests, h[f"table{g}"].reshape(self.batch, self.width))
-        self.dev.copy_(self.hosts[turn], non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        self.copied[turn] = event
+    def run(self, pack: Packer, packed: Optional[Callable[[], None]]) -> torch.Tensor:
+        staging = self.staging
+        turn = staging.take()
+        layout = _rt.StepLayout()
+        total = pack(self.width, self.batch, staging.views[turn], layout)
+        if total != self.layout.total_ints or layout.table[0] != self.layout.table[0]:
+            raise RuntimeError("decode graph: the packed step does not have the captured layout")
+        if packed is not None:
+            packed()
+        self.dev.copy_(staging.hosts[turn], non_blocking=True)
+        staging.queued(turn)
         self.graph.replay()
         return self.logits

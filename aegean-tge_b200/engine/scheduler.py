@@ -22,20 +22,31 @@ and adds what a paged cache needs:
 
 Decisions depend only on the queue and the pools, never on time, so a run can
 be replayed.  The scheduler needs no GPU: it talks to the cache manager and
-hands out :class:`Portion` lists; whoever runs them reports the sampled
-tokens back through :meth:`update`.
+hands out plans; whoever runs them reports the sampled tokens back through
+:meth:`update`.
+
+The queues, the planning and the bookkeeping are C++ (csrc/runtime.cpp:
+``TgeRtScheduler``), which also keeps each request's tokens so that a plan can
+be packed into the step's index arrays without passing through Python lists.
+:class:`Request` here carries what the sampler needs (parameters, generator
+state, the tokens generated so far) and mirrors the rest.
 """
 from __future__ import annotations
 
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
+
+from .. import runtime as _rt
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams, XorShift32
 from .batch import Portion
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+_STATES = (WAITING, RUNNING, FINISHED)
+_REASONS = ("end_token", "length", "context")
 
 
 @dataclass
@@ -45,11 +56,10 @@ class Request:
     max_new_tokens: int
     sampling: SamplingParams = field(default_factory=SamplingParams)
     output: List[int] = field(default_factory=list)
-    state: str = WAITING
-    computed: int = 0                 # tokens whose cache entries exist
     finish_reason: Optional[str] = None
-    preemptions: int = 0
     rng: XorShift32 = field(default_factory=XorShift32)
+    _scheduler: Optional["Scheduler"] = field(default=None, repr=False, compare=False)
+    _last: tuple = field(default=(WAITING, 0, 0), repr=False, compare=False)   # state, computed, preemptions at finish
 
     def __post_init__(self) -> None:
         self.rng = XorShift32(self.sampling.seed)
@@ -61,6 +71,24 @@ class Request:
     @property
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
+
+    def _info(self) -> tuple:
+        if self._scheduler is None:
+            return self._last
+        return self._scheduler._info(self.id)
+
+    @property
+    def state(self) -> str:
+        return self._info()[0]
+
+    @property
+    def computed(self) -> int:
+        """Tokens whose cache entries exist."""
+        return self._info()[1]
+
+    @property
+    def preemptions(self) -> int:
+        return self._info()[2]
 
     def token_slice(self, start: int, count: int) -> List[int]:
         """Tokens [start, start + count) of prompt-then-output, without building the whole list."""
@@ -84,6 +112,7 @@ class ScheduledPortion:
 class StepPlan:
     items: List[ScheduledPortion] = field(default_factory=list)
     preempted: List[Hashable] = field(default_factory=list)
+    scheduler: Optional["Scheduler"] = field(default=None, repr=False)
 
     @property
     def num_tokens(self) -> int:
@@ -95,6 +124,12 @@ class StepPlan:
             tokens = item.request.token_slice(item.start, item.count)
             out.append(Portion(item.request.id, tokens, [item.count - 1] if item.samples else []))
         return out
+
+    def pack(self, vocab_size: int, fixed_width: int, pad_rows: int, out: np.ndarray, layout: "_rt.StepLayout") -> int:
+        """Packs the plan's index arrays into ``out`` (int32) straight from the runtime's own token copies."""
+        s = self.scheduler
+        return _rt.check(s._lib.tge_rt_sched_pack(s._native, int(vocab_size), int(fixed_width), int(pad_rows),
+                                                  out.ctypes.data, out.size, ctypes.byref(layout)))
 
 
 class Scheduler:
@@ -109,133 +144,127 @@ class Scheduler:
         self.max_requests = min(max_requests, cache.max_requests)
         self.max_model_len = max_model_len
         self.chunk = chunk
-        self.end_token_ids = frozenset(end_token_ids)
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []          # in admission order
+        self.end_token_ids = frozenset(int(t) for t in end_token_ids)
+        self._lib = _rt.lib()
+        ends = (ctypes.c_int * max(len(self.end_token_ids), 1))(*sorted(self.end_token_ids))
+        self._native = self._lib.tge_rt_sched_create(cache.native, int(max_batch_tokens), int(max_requests),
+                                                     int(max_model_len), int(chunk or 0), ends, len(self.end_token_ids))
+        if not self._native:
+            _rt.check(_rt.VALUE_ERROR)
+        self._requests: Dict[Hashable, Request] = {}          # waiting or running
         self.finished: Dict[Hashable, Request] = {}
-        self.counters = {"steps": 0, "tokens": 0, "preemptions": 0, "admitted": 0, "finished": 0}
+        most = max(self.max_requests, 1)
+        self._ids = (ctypes.c_int64 * most)()
+        self._starts = (ctypes.c_int * most)()
+        self._counts = (ctypes.c_int * most)()
+        self._samples = (ctypes.c_int * most)()
+        self._reasons = (ctypes.c_int * most)()
+
+    def __del__(self):
+        if getattr(self, "_native", None):
+            self._lib.tge_rt_sched_destroy(self._native)
+            self._native = None
+
+    # -- views ----------------------------------------------------------------
+    def _info(self, request: Hashable) -> tuple:
+        state, computed, preemptions, tokens = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        _rt.check(self._lib.tge_rt_sched_request_info(self._native, self.cache.handle_of(request), ctypes.byref(state),
+                                                      ctypes.byref(computed), ctypes.byref(preemptions),
+                                                      ctypes.byref(tokens)))
+        return _STATES[state.value], computed.value, preemptions.value
+
+    def _listed(self, function) -> List[Request]:
+        count = function(self._native, self._ids, len(self._ids))
+        if count > len(self._ids):
+            self._ids = (ctypes.c_int64 * count)()
+            count = function(self._native, self._ids, count)
+        return [self._requests[self.cache.name_of(h)] for h in self._ids[:count]]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._listed(self._lib.tge_rt_sched_waiting)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._listed(self._lib.tge_rt_sched_running)
+
+    @property
+    def counters(self) -> Dict[str, int]:
+        names = ("steps", "tokens", "preemptions", "admitted", "finished")
+        return {name: int(self._lib.tge_rt_sched_counter(self._native, i)) for i, name in enumerate(names)}
 
     # -- submission -----------------------------------------------------------
     def add(self, request: Request) -> None:
         request.sampling.validate()
-        if not request.prompt:
-            raise ValueError(f"request {request.id!r}: at least one prompt token is required")
-        if request.max_new_tokens <= 0:
-            raise ValueError(f"request {request.id!r}: max_new_tokens must be positive")
-        if len(request.prompt) + 1 > self.max_model_len:
-            raise ValueError(f"request {request.id!r}: {len(request.prompt)} prompt tokens leave no room in a "
-                             f"context of {self.max_model_len}")
-        # the last generated token is never fed back, so a request caches at most prompt + new - 1 tokens
-        most = min(len(request.prompt) + request.max_new_tokens - 1, self.max_model_len)
-        if not self.cache.fits_empty_pool(most):
-            raise ValueError(f"request {request.id!r}: {most} tokens do not fit the page pool even when it is empty")
-        if any(r.id == request.id for r in self.waiting) or any(r.id == request.id for r in self.running):
+        if request.id in self._requests:
             raise ValueError(f"request id {request.id!r} is already in use")
-        request.state = WAITING
-        self.waiting.append(request)
+        prompt = np.ascontiguousarray(request.prompt, dtype=np.int32)
+        known = request.id in self.cache._handles
+        handle = self.cache.pin(request.id)
+        try:
+            _rt.check(self._lib.tge_rt_sched_add(self._native, handle, prompt.ctypes.data, int(prompt.size),
+                                                 int(request.max_new_tokens)))
+        except Exception:
+            if not known:
+                self.cache.unpin(request.id)
+            raise
+        request._scheduler = self
+        self._requests[request.id] = request
+        self.finished.pop(request.id, None)
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.tge_rt_sched_has_work(self._native))
 
     # -- one step's plan ------------------------------------------------------
-    def _portion_size(self, request: Request, budget: int) -> int:
-        remaining = request.num_tokens - request.computed
-        count = min(remaining, budget)
-        if self.chunk is not None:
-            count = min(count, self.chunk)
-        return count
-
-    def _preempt(self, request: Request, plan: StepPlan) -> None:
-        self.cache.free(request.id)
-        self.running.remove(request)
-        request.state = WAITING
-        request.computed = 0
-        request.preemptions += 1
-        self.waiting.appendleft(request)
-        plan.preempted.append(request.id)
-        plan.items = [item for item in plan.items if item.request is not request]
-        self.counters["preemptions"] += 1
-
     def schedule(self) -> StepPlan:
-        plan = StepPlan()
-        budget = self.max_batch_tokens
-        # running requests first, in admission order; each reserves its pages as it is planned
-        index = 0
-        while index < len(self.running):
-            request = self.running[index]
-            count = self._portion_size(request, budget)
-            if count <= 0:
-                index += 1
-                continue
-            while not self.cache.can_grow(request.id, request.computed + count):
-                victim = self.running[-1]
-                self._preempt(victim, plan)
-                # give the victim's planned tokens back to the budget
-                budget = self.max_batch_tokens - plan.num_tokens
-                if victim is request:
-                    break
-            if request.state != RUNNING:
-                continue                      # it preempted itself; the list is one shorter, same index
-            count = self._portion_size(request, budget)
-            self.cache.grow(request.id, request.computed + count)
-            plan.items.append(ScheduledPortion(request, request.computed, count,
-                                               request.computed + count == request.num_tokens))
-            budget -= count
-            index += 1
-        # then new requests, in arrival order, unless this step had to preempt
-        # (or unless preemption left nothing to run: then the head of the queue starts over at once)
-        while (self.waiting and (not plan.preempted or not plan.items) and budget > 0
-               and len(self.running) < self.max_requests and self.cache.free_slots > 0):
-            request = self.waiting[0]
-            count = self._portion_size(request, budget)
-            pages = -(-count // self.cache.page_size)
-            if any(pages > group.pool.free_count for group in self.cache.groups):
-                break
-            self.waiting.popleft()
-            self.cache.admit(request.id)
-            self.cache.grow(request.id, count)
-            request.state = RUNNING
-            request.computed = 0
-            self.running.append(request)
-            self.counters["admitted"] += 1
-            plan.items.append(ScheduledPortion(request, 0, count, count == request.num_tokens))
-            budget -= count
-        if not plan.items and self.has_work():
-            raise RuntimeError("scheduler: nothing can run although requests are waiting "
-                               "(the page pool is too small for the oldest request's next portion)")
-        self.counters["steps"] += 1
-        self.counters["tokens"] += plan.num_tokens
+        count = self._lib.tge_rt_sched_schedule(self._native)
+        if count < 0:
+            _rt.check(count)
+        if count > len(self._starts):
+            self._ids = (ctypes.c_int64 * count)()
+            self._starts, self._counts = (ctypes.c_int * count)(), (ctypes.c_int * count)()
+            self._samples, self._reasons = (ctypes.c_int * count)(), (ctypes.c_int * count)()
+        self._lib.tge_rt_sched_plan(self._native, self._ids, self._starts, self._counts, self._samples, count)
+        name_of, requests = self.cache._names, self._requests
+        plan = StepPlan(scheduler=self)
+        plan.items = [ScheduledPortion(requests[name_of[self._ids[i]]], self._starts[i], self._counts[i],
+                                       bool(self._samples[i])) for i in range(count)]
+        preempted = self._lib.tge_rt_sched_plan_preempted(self._native, self._ids, len(self._ids))
+        if preempted:
+            plan.preempted = [name_of[h] for h in self._ids[:min(preempted, len(self._ids))]]
+        if self.cache.state_storage:
+            for item in plan.items:           # a request that starts (over) gets a zeroed state slot
+                if item.start == 0:
+                    self.cache.zero_state(self.cache.slot_of(item.request.id))
         return plan
 
     # -- after the step -------------------------------------------------------
     def update(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
         """Records the step: ``sampled`` holds one token per sampling portion, in plan order."""
-        finished: List[Request] = []
+        tokens = np.ascontiguousarray(sampled, dtype=np.int32)
         cursor = 0
         for item in plan.items:
-            request = item.request
-            request.computed = item.start + item.count
-            self.cache.set_computed(request.id, request.computed)
-            if not item.samples:
-                continue
-            token = int(sampled[cursor])
-            cursor += 1
-            request.output.append(token)
-            reason = None
-            if token in self.end_token_ids:
-                reason = "end_token"
-            elif len(request.output) >= request.max_new_tokens:
-                reason = "length"
-            elif request.num_tokens >= self.max_model_len:
-                reason = "context"
-            if reason is not None:
-                request.state = FINISHED
-                request.finish_reason = reason
-                self.cache.free(request.id)
-                self.running.remove(request)
-                self.finished[request.id] = request
-                finished.append(request)
-                self.counters["finished"] += 1
-        if cursor != len(sampled):
-            raise ValueError(f"scheduler: {len(sampled)} sampled tokens for {cursor} sampling portions")
+            if item.samples and cursor < tokens.size:
+                item.request.output.append(int(tokens[cursor]))
+                cursor += 1
+        try:
+            done = _rt.check(self._lib.tge_rt_sched_update(self._native, tokens.ctypes.data, int(tokens.size), self._ids,
+                                                           self._reasons, min(len(self._ids), len(self._reasons))))
+        except Exception:
+            cursor = 0
+            for item in plan.items:           # the step was not recorded: take the tokens back
+                if item.samples and cursor < tokens.size:
+                    item.request.output.pop()
+                    cursor += 1
+            raise
+        finished: List[Request] = []
+        for i in range(done):
+            request = self._requests.pop(self.cache.name_of(self._ids[i]))
+            request.finish_reason = _REASONS[self._reasons[i]]
+            request._last = (FINISHED,) + self._info(request.id)[1:]
+            request._scheduler = None
+            self._lib.tge_rt_sched_forget(self._native, self.cache.handle_of(request.id))
+            self.cache.unpin(request.id)
+            self.finished[request.id] = request
+            finished.append(request)
         return finished
