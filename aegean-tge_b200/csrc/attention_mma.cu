@@ -540,6 +540,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 constexpr int TMA_BLOCKS = HD / 64;                       // 64-column blocks per row
 constexpr int TMA_TILE_BYTES = BKV * HD * 2;              // one K (or V) tile
 constexpr int TMA_STAGE_BYTES = 2 * TMA_TILE_BYTES;
+constexpr int DEC_TMA_THREADS = (DEC_WARPS + 1) * 32;    // computing warps and one loading warp
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
@@ -547,6 +548,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -585,7 +590,7 @@ __device__ __forceinline__ uint32_t swizzled(int row, int col) {
   return (uint32_t)(block * (BKV * 128) + row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
+__global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ unsigned char smem_dyn[];
   pdl_trigger();
@@ -593,7 +598,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzle atoms are 1024 bytes
   unsigned char* generic = smem_dyn + (base - raw);
-  const uint32_t bars = base + DEC_STAGES * TMA_STAGE_BYTES;          // one mbarrier per stage
+  const uint32_t bars = base + DEC_STAGES * TMA_STAGE_BYTES;          // full[stages], then empty[stages]
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (DEC_STAGES + s); };
   int* local_table = reinterpret_cast<int*>(generic + DEC_STAGES * TMA_STAGE_BYTES + 64);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -613,27 +620,30 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
   const int num_tiles = (hi - k_first + BKV - 1) / BKV;
   const int first_page = k_first >> p.page_shift;
   const int last_page = (k_first + num_tiles * BKV - 1) >> p.page_shift;
-  for (int i = first_page + tid; i <= last_page; i += DEC_WARPS * 32) {
+  for (int i = first_page + tid; i <= last_page; i += DEC_TMA_THREADS) {
     int page = i < p.max_pages ? p.block_table[(size_t)seq * p.max_pages + i] : -1;
     if (page >= p.num_pages) page = -2;                                // reported below, never fetched
     local_table[i - first_page] = page;
   }
   {
     uint4* fill = reinterpret_cast<uint4*>(generic);
-    for (int i = tid; i < DEC_STAGES * TMA_STAGE_BYTES / 16; i += DEC_WARPS * 32) fill[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < DEC_STAGES * TMA_STAGE_BYTES / 16; i += DEC_TMA_THREADS) fill[i] = make_uint4(0, 0, 0, 0);
   }
   if (tid == 0) {
-    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(bars + 8 * s, 1);
+    for (int s = 0; s < DEC_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), DEC_WARPS);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // the cleared stages, before TMA writes them
   __syncthreads();
 
   const int pages_per_tile = BKV >> p.page_shift;
-  auto issue = [&](int tile) {                                          // thread 0 only
+  auto issue = [&](int tile) {                                          // the loading warp's first lane only
     const int stage = tile % DEC_STAGES;
     const uint32_t k_dst = base + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
-    const uint32_t bar = bars + 8 * stage;
+    const uint32_t bar = full_bar(stage);
     int boxes = 0;
     for (int j = 0; j < pages_per_tile; ++j) {
       const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
@@ -652,8 +662,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
       }
     }
   };
-  if (tid == 0) {
-    for (int s = 0; s < DEC_STAGES - 1 && s < num_tiles; ++s) issue(s);
+  if (warp == DEC_WARPS) {
+    // The loading warp runs ahead of the others by up to a ring of tiles; nobody waits for anybody else
+    // block-wide.  A stage is refilled once all computing warps have released it.
+    if (lane == 0) {
+      for (int tile = 0; tile < num_tiles; ++tile) {
+        if (tile >= DEC_STAGES)
+          mbar_wait_bounded(empty_bar(tile % DEC_STAGES), (uint32_t)(tile / DEC_STAGES - 1) & 1u, p.status);
+        issue(tile);
+      }
+    }
   }
 
   uint32_t qf[HD / 16][4];
@@ -676,14 +694,17 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   bool bad_page = false;
 
-  for (int it = 0; it < num_tiles; ++it) {
-    __syncthreads();                                     // everyone is done with the stage tile it-1 used
-    if (tid == 0 && it + DEC_STAGES - 1 < num_tiles) issue(it + DEC_STAGES - 1);
+  for (int it = 0; it < (warp < DEC_WARPS ? num_tiles : 0); ++it) {
     const int stage = it % DEC_STAGES;
-    mbar_wait_bounded(bars + 8 * stage, (uint32_t)(it / DEC_STAGES) & 1u, p.status);
-    const uint32_t tK = base + stage * TMA_STAGE_BYTES, tV = tK + TMA_TILE_BYTES;
     const int k0 = k_first + it * BKV + warp * 16;
-    if (k0 >= hi || k0 + 16 <= lo) continue;
+    // every warp sees every copy land, also of tiles it has no visible position in: the parity of a wait
+    // only tells phases apart while nobody is a whole phase behind
+    mbar_wait_bounded(full_bar(stage), (uint32_t)(it / DEC_STAGES) & 1u, p.status);
+    if (k0 >= hi || k0 + 16 <= lo) {
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+      continue;
+    }
+    const uint32_t tK = base + stage * TMA_STAGE_BYTES, tV = tK + TMA_TILE_BYTES;
     if (local_table[(max(k0, lo) >> p.page_shift) - first_page] < 0) bad_page = true;   // a visible position without a page
 
     float s_acc[2][4];
@@ -755,6 +776,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
       mma_bf16(o_acc[dt], pf, r0, r1);
       mma_bf16(o_acc[dt + 1], pf, r2, r3);
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar(stage));        // this warp has read all it needs of the stage
   }
   __syncthreads();                                       // all tiles consumed, no copy in flight: reuse the stages
   if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
@@ -762,7 +785,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
   float* merge_o = reinterpret_cast<float*>(generic);                   // [warps][16][HD]
   float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                      // [warps][16][2]
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < (warp < DEC_WARPS ? 2 : 0); ++i) {
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     const int r = g8 + 8 * i;
@@ -776,7 +799,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < p.group * HD; idx += DEC_WARPS * 32) {
+  for (int idx = tid; idx < p.group * HD; idx += DEC_TMA_THREADS) {
     const int r = idx / HD, d = idx - r * HD;
     float m = -INFINITY;
 #pragma unroll
@@ -812,10 +835,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_tma_kernel(
 constexpr int PRE_WARPS = 8;                  // warps that compute; one more warp issues the TMA loads
 constexpr int PRE_STAGES = 4;
 constexpr int PRE_THREADS = (PRE_WARPS + 1) * 32;
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
 
 __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -1249,7 +1268,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     }
     p.bq = 1;
     dim3 grid(num_seqs, kv_heads, num_splits);
-    tge_launch(attention_decode_tma_kernel, grid, DEC_WARPS * 32, smem, stream, *map_k, *map_v, p);
+    tge_launch(attention_decode_tma_kernel, grid, DEC_TMA_THREADS, smem, stream, *map_k, *map_v, p);
     int rc = tge_check_launch("attention_decode_tma");
     if (rc != 0) return rc;
     if (num_splits > 1) {

@@ -278,6 +278,15 @@ def test_attention_mma_split_keys(ops, split, q_lens, starts):
     assert err < TOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(28, 4, 128), (10, 2, 64), (16, 1, 128)])
+@pytest.mark.parametrize("split,window", [(128, 0), (512, 0), (256, 300), (64, 0), (192, 77)])
+def test_attention_decode_splits(ops, heads, kv_heads, head_dim, split, window):
+    """Single tokens with two to sixteen key splits, some of them without keys for the short requests."""
+    err, _, _ = _attention_case(ops, torch.bfloat16, heads, kv_heads, head_dim, [1, 1, 1, 1, 1], [1000, 0, 511, 512, 130],
+                                window=window, split=split)
+    assert err < TOL[torch.bfloat16]
+
+
 @pytest.mark.parametrize("dtype,simt", [(torch.float32, True), (torch.bfloat16, True), (torch.bfloat16, False)])
 def test_attention_reads_a_far_key(ops, dtype, simt):
     """One key hundreds of positions back carries almost all the weight: the output must be its value."""
