@@ -5,6 +5,7 @@
     tge generate --model DIR --tokens "a b c" [--n N] [--temp T] [--top-k N] [--top-p P] [--min-p P]
                  [--repeat-penalty R] [--penalty-window N] [--seed N] [--context N] [--print-ids]
     tge bench prefill|decode --model DIR [--prompt-len N] [--batch B] [--n N] [--repeat R]
+    tge bench continuous --model DIR [--requests N] [--tokens N] [--sequences N] [--prompt-tokens N] [--prompt-max N]
     tge make-random --config FILE --out DIR [--seed S] [--dtype float32|bfloat16]
     tge replay --model DIR --dtype D --out DIR --max-tokens N          (same as bin/trace_run)
     tge version
@@ -82,12 +83,18 @@ def build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--print-ids", action="store_true", help="print generated token ids")
     generate.add_argument("--text", action="store_true", help="(needs a tokenizer: not supported)")
     bench = commands.add_parser("bench", help="prefill or decode throughput with its roofline fraction")
-    bench.add_argument("what", choices=["prefill", "decode"])
+    bench.add_argument("what", choices=["prefill", "decode", "continuous"])
     _model_args(bench)
     bench.add_argument("--prompt-len", type=int, default=2048)
     bench.add_argument("--batch", type=int, default=1)
     bench.add_argument("--n", type=int, default=64, help="decode steps to time")
     bench.add_argument("--repeat", type=int, default=3)
+    # bench continuous, with the reference's names (apps/cli/main.cpp:2825-2890)
+    bench.add_argument("--requests", type=int, default=8, help="continuous: requests to serve (default 8)")
+    bench.add_argument("--tokens", type=int, default=32, help="continuous: tokens generated per request (default 32)")
+    bench.add_argument("--sequences", type=int, default=4, help="continuous: requests live at a time (default 4)")
+    bench.add_argument("--prompt-tokens", type=int, default=1, help="continuous: prompt length (default 1)")
+    bench.add_argument("--prompt-max", type=int, help="continuous: draw each prompt's length from [prompt-tokens, this]")
     make = commands.add_parser("make-random", help="write a model folder with seeded random weights")
     make.add_argument("--config", required=True, help="a config.json")
     make.add_argument("--out", required=True)
@@ -236,8 +243,75 @@ def command_generate(args) -> int:
     return 0
 
 
+def command_bench_continuous(args) -> int:
+    """Continuous batching as the reference's ``bench continuous`` runs it (apps/cli/main.cpp:1451-1644):
+    ``requests`` requests through ``sequences`` live slots, greedy, ``tokens`` new tokens each.  With one
+    prompt for all (the default) the transcripts must be identical whatever shared a step with what; with
+    ``--prompt-max`` the prompts differ in length and content and only the rate is reported."""
+    import random
+    import time
+    import torch
+    if min(args.requests, args.tokens, args.sequences, args.prompt_tokens) <= 0:
+        raise UsageError("bench continuous: requests, tokens, sequences and prompt-tokens must be positive")
+    if args.prompt_max is not None and args.prompt_max < args.prompt_tokens:
+        raise UsageError("bench continuous: --prompt-max must not be below --prompt-tokens")
+    args.max_requests = args.sequences
+    started = time.time()
+    engine = _engine_from(args)
+    load_seconds = time.time() - started
+    longest = args.prompt_max or args.prompt_tokens
+    if longest + args.tokens > engine.max_model_len:
+        raise UsageError(f"bench continuous: prompt-tokens + tokens ({longest + args.tokens}) exceeds the "
+                         f"{engine.max_model_len}-token context")
+    rnd = random.Random(1234)
+    vocab = engine.spec.vocab_size
+    seed_prompt = [rnd.randrange(vocab) for _ in range(args.prompt_tokens)]
+    prompts = []
+    for _ in range(args.requests):
+        if args.prompt_max is None:
+            prompts.append(seed_prompt)
+        else:
+            prompts.append([rnd.randrange(vocab) for _ in range(rnd.randint(args.prompt_tokens, args.prompt_max))])
+    ids = [engine.add_request(p, args.tokens) for p in prompts]
+    torch.cuda.synchronize()
+    begin = time.time()
+    done = {}
+    steps = 0
+    while engine.has_unfinished():
+        for request in engine.step():
+            done[request.id] = request
+        steps += 1
+    torch.cuda.synchronize()
+    seconds = time.time() - begin
+    transcripts = [done[i].output for i in ids]
+    generated = sum(len(t) for t in transcripts)
+    prompt_total = sum(len(p) for p in prompts)
+    stats = engine.stats()
+    print(f"continuous: {args.requests} requests, {args.sequences} slots, {args.tokens} tokens")
+    print(f"load      : {load_seconds * 1e3:.1f} ms")
+    print(f"wall      : {seconds:.3f} s in {steps} steps ({stats['preemptions']} preemptions)")
+    print(f"prompts   : {prompt_total} tokens, lengths {min(map(len, prompts))}..{max(map(len, prompts))}")
+    print(f"decode    : {generated} tokens, {generated / seconds:.2f} t/s aggregate "
+          f"({(generated + prompt_total) / seconds:.1f} t/s with the prompts)")
+    if args.prompt_max is None:
+        identical = all(t == transcripts[0] for t in transcripts)
+        if identical:
+            print("state     : independent (all transcripts identical)")
+        elif engine.dtype == torch.float32:
+            print("state     : LEAKED - transcripts differ")
+        else:
+            print("state     : transcripts differ (bfloat16 rounds differently in different batches and may flip a "
+                  "near-tie; --dtype float32 is exact)")
+        print("first     : " + " ".join(str(t) for t in transcripts[0][:32]) + (" ..." if len(transcripts[0]) > 32 else ""))
+        return 0 if identical or engine.dtype != torch.float32 else 1
+    print("state     : not compared (prompts differ)")
+    return 0
+
+
 def command_bench(args) -> int:
     from .bench_tools import bench_decode, bench_prefill
+    if args.what == "continuous":
+        return command_bench_continuous(args)
     engine = _engine_from(args)
     if args.what == "prefill":
         result = bench_prefill(engine, args.prompt_len, repeat=args.repeat)

@@ -24,13 +24,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # The Qwen2.5-7B shape of BASELINE.json's configs[2]
-CONFIG_7B = {
-    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
-    "num_hidden_layers": 28, "hidden_size": 3584, "num_attention_heads": 28, "num_key_value_heads": 4,
-    "head_dim": 128, "intermediate_size": 18944, "vocab_size": 152064, "rope_theta": 1000000.0,
-    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 32768,
-    "use_sliding_window": False, "hidden_act": "silu",
-}
+with open(os.path.join(ROOT, "aegean-tge_b200", "config", "shapes", "qwen2.5-7b.json"), "r", encoding="utf-8") as _handle:
+    CONFIG_7B = json.load(_handle)
 PROMPT = 2048
 CONTEXT = 4096
 BATCH = 8

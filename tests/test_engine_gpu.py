@@ -267,3 +267,18 @@ def test_tensor_core_and_cuda_core_paths_agree_at_a_large_layer_shape():
         ops.USE_TCGEN05, ops.USE_MMA_ATTENTION = True, True
     ops.check_status()
     assert rel_error(fast, slow) < MODEL_TOL["bfloat16"]
+
+
+def test_bench_continuous_transcripts_are_identical(model_dirs, capsys):
+    """The reference's leak check (apps/cli/main.cpp:1620-1643): every request gets the same prompt, more
+    requests than slots, so requests start beside others at every stage; in float32 all transcripts are equal."""
+    from aegean_tge_b200.cli import main
+    code = main(["bench", "continuous", "--model", model_dirs["B"], "--dtype", "float32", "--requests", "7",
+                 "--sequences", "3", "--tokens", "12", "--prompt-tokens", "21", "--context", "128", "--num-pages", "9",
+                 "--max-batch-tokens", "16"])
+    out = capsys.readouterr().out
+    assert code == 0, out
+    assert "independent (all transcripts identical)" in out and "7 requests, 3 slots" in out
+    code = main(["bench", "continuous", "--model", model_dirs["A"], "--requests", "5", "--sequences", "2", "--tokens", "6",
+                 "--prompt-tokens", "3", "--prompt-max", "40", "--context", "128"])
+    assert code == 0 and "not compared" in capsys.readouterr().out
