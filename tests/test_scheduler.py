@@ -138,3 +138,56 @@ def test_a_lone_request_that_fits_always_progresses():
     plans = _run(s, cache)
     assert s.finished["a"].state == FINISHED and len(s.finished["a"].output) == 9
     assert all(not p.preempted for p in plans)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_finish_with_the_same_outputs_whatever_the_pool(seed):
+    """Requests of random sizes arrive at random times into pools from roomy to barely sufficient, with random
+    budgets and portion caps.  Every request finishes with the tokens a function of (request, position)
+    dictates, nothing is lost or held twice on the way, and the packed step matches the plan."""
+    import random
+
+    import numpy as np
+
+    from aegean_tge_b200 import runtime as rt
+    rnd = random.Random(seed)
+    specs = [(f"r{i}", rnd.randint(1, 70), rnd.randint(1, 25)) for i in range(rnd.randint(3, 12))]
+    largest = max(-(-(p + n - 1) // 16) for _, p, n in specs)
+    expected = {name: [(7 * len(name) + 13 * p + 31 * k) % 97 for k in range(n)] for name, p, n in specs}
+    for pages in (largest, largest + 2, 64):
+        cache, s = _setup(pages, slots=rnd.randint(1, 4), max_batch_tokens=rnd.choice([3, 8, 16, 64]),
+                          max_requests=rnd.randint(1, 4), chunk=rnd.choice([None, 2, 5, 16]), max_model_len=128)
+        arrivals = sorted((rnd.randint(0, 30), spec) for spec in specs)
+        out = np.zeros(4096, dtype=np.int32)
+        layout = rt.StepLayout()
+        step = 0
+        while arrivals or s.has_work():
+            while arrivals and arrivals[0][0] <= step:
+                _, (name, p, n) = arrivals.pop(0)
+                s.add(Request(name, [(3 * i + len(name)) % 97 for i in range(p)], n))
+            step += 1
+            if not s.has_work():
+                continue
+            plan = s.schedule()
+            assert plan.num_tokens <= s.max_batch_tokens and plan.items
+            plan.pack(97, 0, 0, out, layout)
+            assert layout.num_tokens == plan.num_tokens and layout.num_seqs == len(plan.items)
+            assert layout.num_rows == sum(i.samples for i in plan.items)
+            cursor = layout.token_ids
+            for index, item in enumerate(plan.items):
+                tokens = item.request.token_slice(item.start, item.count)
+                assert out[cursor:cursor + item.count].tolist() == tokens
+                assert out[layout.start_pos + index] == item.start == cache.computed(item.request.id)
+                assert out[layout.slots + index] == cache.slot_of(item.request.id)
+                table = cache.groups[0].tables[item.request.id]
+                width = layout.width[0]
+                row = out[layout.table[0] + index * width:layout.table[0] + (index + 1) * width].tolist()
+                assert row[:len(table)] == table and all(x == -1 for x in row[len(table):])
+                cursor += item.count
+            sampled = [expected[i.request.id][len(i.request.output)] for i in plan.items if i.samples]
+            s.update(plan, sampled)
+            cache.check()
+            assert step < 5000
+        assert {name: s.finished[name].output for name in expected} == expected
+        assert cache.free_slots == cache.max_requests and cache.groups[0].pool.free_count == pages
+        assert not cache._handles, "id mappings of finished requests are dropped"
