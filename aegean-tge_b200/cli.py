@@ -46,7 +46,8 @@ def _model_args(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     parser.add_argument("--context", type=int, default=4096, help="KV cache length (default 4096, capped by model)")
-    parser.add_argument("--num-pages", type=int, help="pages of 16 tokens in the cache pool (default: from free memory)")
+    parser.add_argument("--num-pages", type=int, help="pages in the cache pool (default: from free memory)")
+    parser.add_argument("--page-size", type=int, default=None, help="tokens per page: 64 (default), 32, 16 or 8")
     parser.add_argument("--max-batch-tokens", type=int, default=2048, help="token budget of one step")
     parser.add_argument("--chunk", type=int, help="largest prompt portion in one step (default: the budget)")
     parser.add_argument("--max-requests", type=int, default=64)
@@ -119,14 +120,16 @@ def _engine_from(args):
             random_config = json.load(handle)
     return Engine(args.model, random_config=random_config, seed=args.weights_seed, dtype=args.dtype,
                   context=args.context, num_pages=args.num_pages, max_batch_tokens=args.max_batch_tokens,
-                  chunk=args.chunk, max_requests=args.max_requests)
+                  chunk=args.chunk, max_requests=args.max_requests,
+                  **({} if args.page_size is None else {"page_size": args.page_size}))
 
 
 def command_info(args) -> int:
     import torch
     from .csrc import build
+    from .engine.engine import PAGE_SIZE
     facts = {"version": __version__, "cuda_available": torch.cuda.is_available(), "torch": torch.__version__,
-             "cuda_runtime": torch.version.cuda, "page_size": 16, "kernel_target": "sm_100a",
+             "cuda_runtime": torch.version.cuda, "page_size": PAGE_SIZE, "kernel_target": "sm_100a",
              "kernel_sources": build.CORE_SOURCES + ["attention_mma.cu"]}
     if torch.cuda.is_available():
         props = torch.cuda.get_device_properties(0)

@@ -12,16 +12,21 @@
 //      into shared memory in the K-major swizzled layout, over the K tile that step 2 has finished with;
 //   4. the issuing thread adds P V (V is MN-major in shared memory: head dimension contiguous) into the
 //      output accumulator in columns [64, 64 + head_dim);
-//   5. a row whose running maximum rose rescales its accumulator in tensor memory (tcgen05.ld, multiply,
-//      tcgen05.st) before the next product is added; rows read their output once, at the end.
-// Two blocks fit on an SM, so one block's softmax overlaps the other's products.
+//   5. a row whose running maximum rose by more than 2^8 rescales its accumulator in tensor memory
+//      (tcgen05.ld, multiply, tcgen05.st) before the next product is added; smaller rises keep the old
+//      reference (probabilities then reach up to 256, which bfloat16 and the float32 sums hold without
+//      loss); rows read their output once, at the end.
+// Six warps: four do the softmax (one row per thread), one issues the products, one issues the TMA
+// copies, its lanes one box each - a single thread that does both spends most of a tile's time issuing
+// copies.  Two blocks fit on an SM, so one block's softmax overlaps the other's products.
 // Masking, splits along the keys and the output layout are those of the other attention kernels.
 #pragma once
 
 namespace tc {
 
 constexpr int ROWS = 128;
-constexpr int THREADS = 160;                       // four softmax warps and one warp that loads and issues
+constexpr int THREADS = 192;                       // four softmax warps, one warp that issues products, one that issues copies
+constexpr float RESCALE_STEP = 8.0f;               // in powers of two: how far a row's maximum may rise before its reference moves
 constexpr int STAGES = 2;
 constexpr int Q_BYTES = ROWS * HD * 2;
 constexpr int P_BYTES = ROWS * BKV * 2;            // 16 KiB
@@ -63,6 +68,35 @@ __device__ __forceinline__ void store32(uint32_t taddr, const uint32_t r[32]) {
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
+// Two float32 lanes at a time (sm_100 has paired FMA and ADD), one MUFU exponential, three-input maximum:
+// the softmax warps are bound by the number of instructions they issue per score.
+__device__ __forceinline__ uint64_t pair(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float ex2(float x) {       // 2^x; arguments are <= 0 here, tiny results flush to zero
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // K-major operand: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
@@ -88,8 +122,10 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   const uint32_t p_own = base + Q_BYTES;                                   // used only when P does not fit over K
   const uint32_t stages = base + Q_BYTES + (P_OVER_K ? 0 : P_BYTES);
   const uint32_t bars = stages + STAGES * TMA_STAGE_BYTES;
-  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, s_bar = bars + 16 * STAGES, p_bar = s_bar + 16, o_bar = s_bar + 24;   // s_bar: one per score buffer
-  int* local_table = reinterpret_cast<int*>(generic + (stages - base) + STAGES * TMA_STAGE_BYTES + 64);
+  // full_bar: K of a stage has landed; v_bar: V has; s_bar: one per score buffer
+  const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES, s_bar = bars + 16 * STAGES, p_bar = s_bar + 16, o_bar = s_bar + 24,
+                 v_bar = s_bar + 32;
+  int* local_table = reinterpret_cast<int*>(generic + (stages - base) + STAGES * TMA_STAGE_BYTES + 128);   // after the barriers
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = blockIdx.y, split = blockIdx.z;
@@ -155,6 +191,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar + 8 * s, 1);
+      mbar_init(v_bar + 8 * s, 1);
       mbar_init(empty_bar + 8 * s, 1);
     }
     mbar_init(s_bar, 1);
@@ -175,70 +212,76 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   pdl_trigger();                                                      // tensor memory is held: the next kernel may be scheduled
   const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + 2 * BKV;
 
-  if (warp == 4) {
+  if (warp == 5) {
+    // ------------------------------- copies: one box per lane -------------------------------
+    // A tile is (pages per tile) x (64-column blocks) x (K, V) boxes.  Each lane takes boxes of its own;
+    // the first lane announces the bytes of those that will really be fetched.
+    const int pages_per_tile = BKV >> p.page_shift;
+    const int boxes = pages_per_tile * TMA_BLOCKS * 2;
+    for (int tile = 0; tile < num_tiles; ++tile) {
+      const int stage = tile % STAGES;
+      if (tile >= STAGES) mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(tile / STAGES - 1) & 1u, p.status);
+      const uint32_t k_dst = stages + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
+      const int tile_first = k_first + tile * BKV;
+      int wanted = 0;
+      for (int j = lane; j < pages_per_tile; j += 32) {
+        const int page = local_table[(tile_first >> p.page_shift) + j - first_page];
+        if (page >= 0 && tile_first + (j << p.page_shift) < hi) ++wanted;
+      }
+      wanted = __reduce_add_sync(0xffffffffu, wanted);
+      if (lane == 0) {
+        mbar_expect_tx(full_bar + 8 * stage, (uint32_t)wanted * TMA_BLOCKS * (uint32_t)(p.page_size * 128));
+        mbar_expect_tx(v_bar + 8 * stage, (uint32_t)wanted * TMA_BLOCKS * (uint32_t)(p.page_size * 128));
+      }
+      __syncwarp();
+      // K's boxes first: the scores of the tile can start while V is still on its way
+      for (int box = lane; box < boxes; box += 32) {
+        const int which = box >= boxes / 2, rest = box - which * (boxes / 2);
+        const int b = rest % TMA_BLOCKS, j = rest / TMA_BLOCKS;
+        const uint32_t bar = (which ? v_bar : full_bar) + 8 * stage;
+        const int page = local_table[(tile_first >> p.page_shift) + j - first_page];
+        if (page < 0 || tile_first + (j << p.page_shift) >= hi) continue;
+        const int row = (page * p.kv_heads + kvh) << p.page_shift;
+        const uint32_t offset = (uint32_t)(b * (BKV * 128) + (j << p.page_shift) * 128);
+        tma_load_2d((which ? v_dst : k_dst) + offset, which ? &map_v : &map_k, bar, b * 64, row);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------- products -------------------------------
     if (lane == 0) {
-      const int pages_per_tile = BKV >> p.page_shift;
-      auto issue_loads = [&](int tile) {
-        const int stage = tile % STAGES;
-        const uint32_t k_dst = stages + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
-        const uint32_t bar = full_bar + 8 * stage;
-        int boxes = 0;
-        for (int j = 0; j < pages_per_tile; ++j) {
-          const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
-          if (page >= 0 && (k_first + tile * BKV + (j << p.page_shift)) < hi) ++boxes;
-        }
-        mbar_expect_tx(bar, (uint32_t)boxes * 2u * TMA_BLOCKS * (uint32_t)(p.page_size * 128));
-        for (int j = 0; j < pages_per_tile; ++j) {
-          const int page = local_table[((k_first + tile * BKV) >> p.page_shift) + j - first_page];
-          if (page < 0 || (k_first + tile * BKV + (j << p.page_shift)) >= hi) continue;
-          const int row = (page * p.kv_heads + kvh) << p.page_shift;
-#pragma unroll
-          for (int b = 0; b < TMA_BLOCKS; ++b) {
-            const uint32_t offset = (uint32_t)(b * (BKV * 128) + (j << p.page_shift) * 128);
-            tma_load_2d(k_dst + offset, &map_k, bar, b * 64, row);
-            tma_load_2d(v_dst + offset, &map_v, bar, b * 64, row);
-          }
-        }
-      };
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
-      // S = Q K^T of one tile into score buffer (tile & 1)
+      const uint64_t q_desc = desc_k_major(q_smem);
+      // S = Q K^T of one tile into score buffer (tile & 1); descriptors move by (byte offset >> 4)
       auto issue_scores = [&](int tile) {
         const int stage = tile % STAGES;
         mbar_wait_bounded(full_bar + 8 * stage, (uint32_t)(tile / STAGES) & 1u, p.status);
         fence_after();
-        const uint32_t k_tile = stages + stage * TMA_STAGE_BYTES;
+        const uint64_t k_desc = desc_k_major(stages + stage * TMA_STAGE_BYTES);
         const uint32_t d_tmem = s_tmem + (uint32_t)((tile & 1) * BKV);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t block = ks >> 2, step = ks & 3;
-          mma(d_tmem, desc_k_major(q_smem + block * (ROWS * 128) + step * 32),
-              desc_k_major(k_tile + block * (BKV * 128) + step * 32), idesc_s, ks > 0 ? 1u : 0u);
+          mma(d_tmem, q_desc + ((block * (ROWS * 128) + step * 32) >> 4), k_desc + ((block * (BKV * 128) + step * 32) >> 4),
+              idesc_s, ks > 0 ? 1u : 0u);
         }
         commit(s_bar + 8 * (tile & 1));
       };
-      issue_loads(0);
-      if (num_tiles > 1) issue_loads(1);
       issue_scores(0);
       for (int it = 0; it < num_tiles; ++it) {
         const int stage = it % STAGES;
         // the next tile's scores are computed while the softmax warps work on this tile's
         if (it + 1 < num_tiles) issue_scores(it + 1);
         mbar_wait_bounded(p_bar, (uint32_t)it & 1u, p.status);
+        mbar_wait_bounded(v_bar + 8 * stage, (uint32_t)(it / STAGES) & 1u, p.status);
         fence_after();
         const uint32_t k_tile = stages + stage * TMA_STAGE_BYTES, v_tile = k_tile + TMA_TILE_BYTES;
-        const uint32_t p_tile = P_OVER_K ? k_tile : p_own;
+        const uint64_t p_desc = desc_k_major(P_OVER_K ? k_tile : p_own), v_desc = desc_mn_major(v_tile, BKV * 128);
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks)
-          mma(o_tmem, desc_k_major(p_tile + ks * 32), desc_mn_major(v_tile + ks * (16 * 128), BKV * 128), idesc_o,
-              (it > 0 || ks > 0) ? 1u : 0u);
+          mma(o_tmem, p_desc + ((ks * 32) >> 4), v_desc + ((ks * (16 * 128)) >> 4), idesc_o, (it > 0 || ks > 0) ? 1u : 0u);
         commit(o_bar);
-        commit(empty_bar + 8 * stage);
-        if (it + STAGES < num_tiles) {
-          // this tile's stage is free once its product has been read: refill it for tile it + 2
-          mbar_wait_bounded(empty_bar + 8 * stage, (uint32_t)(it / STAGES) & 1u, p.status);
-          issue_loads(it + STAGES);
-        }
+        commit(empty_bar + 8 * stage);      // the stage is free once this product has read P and V
       }
     }
   } else {
@@ -248,7 +291,8 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
     // is added (a whole warp does it together, rows whose maximum stood still use a factor of one).
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const int first_key = p.window > 0 ? row_pos - p.window + 1 : 0;
-    float m_run = -INFINITY, l_run = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;            // m_run: the row's reference, in raw score units
+    const float step_raw = RESCALE_STEP / p.scale_log2;
     bool bad_page = false;
     for (int it = 0; it < num_tiles; ++it) {
       const int stage = it % STAGES;
@@ -266,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       float mx = -INFINITY;
       if (__all_sync(0xffffffffu, whole)) {
 #pragma unroll
-        for (int j = 0; j < BKV; ++j) mx = fmaxf(mx, __uint_as_float(s_bits[j]));
+        for (int j = 0; j < BKV; j += 2) mx = max3(mx, __uint_as_float(s_bits[j]), __uint_as_float(s_bits[j + 1]));
       } else {
 #pragma unroll
         for (int j = 0; j < BKV; ++j) {
@@ -277,11 +321,16 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
           mx = fmaxf(mx, sv);
         }
       }
-      const float m_new = fmaxf(m_run, mx);
+      // The reference that exponents are taken against moves only when the maximum rose by more than
+      // RESCALE_STEP powers of two (or nothing was visible so far): the accumulator in tensor memory is
+      // then seldom rescaled after the first tiles.
+      const bool moved = mx > m_run + step_raw || m_run == -INFINITY;
+      const float m_new = moved ? mx : m_run;
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
       const float corr = exp2f((m_run - m_use) * p.scale_log2);            // exp2(-inf) = 0 while nothing was visible yet
       const float shift = -m_use * p.scale_log2;
-      float sum = 0.0f;
+      const uint64_t scale2 = pair(p.scale_log2, p.scale_log2), shift2 = pair(shift, shift);
+      uint64_t sum2 = pair(0.0f, 0.0f);
       const uint32_t p_row = (P_OVER_K ? stages + stage * TMA_STAGE_BYTES : p_own) + r * 128;
       if (!P_OVER_K && it > 0) {
         // P has one buffer of its own here: the previous tile's product must have read it
@@ -292,16 +341,21 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       for (int c = 0; c < BKV / 8; ++c) {
         float pv[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          pv[e] = exp2f(fmaf(__uint_as_float(s_bits[c * 8 + e]), p.scale_log2, shift));
-          sum += pv[e];
+        for (int e = 0; e < 8; e += 2) {
+          float a, b;
+          unpair(fma2(pair(__uint_as_float(s_bits[c * 8 + e]), __uint_as_float(s_bits[c * 8 + e + 1])), scale2, shift2), a, b);
+          pv[e] = ex2(a);               // a masked score is -inf: 2^-inf = 0
+          pv[e + 1] = ex2(b);
+          sum2 = add2(sum2, pair(pv[e], pv[e + 1]));
         }
         const uint32_t dst = p_row + ((c ^ (r & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(pack_bf16(pv[0], pv[1])),
                      "r"(pack_bf16(pv[2], pv[3])), "r"(pack_bf16(pv[4], pv[5])), "r"(pack_bf16(pv[6], pv[7])) : "memory");
       }
-      l_run = l_run * corr + sum;
-      const bool rescale = it > 0 && m_new > m_run && m_run != -INFINITY;
+      float sum_even, sum_odd;
+      unpair(sum2, sum_even, sum_odd);
+      l_run = l_run * corr + (sum_even + sum_odd);
+      const bool rescale = it > 0 && moved && m_run != -INFINITY;
       m_run = m_new;
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");   // P, before the tensor core reads it
       if (it > 0) {
@@ -366,7 +420,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
 }
 
 constexpr size_t smem_bytes(int table_entries) {
-  return 1024 + Q_BYTES + (P_OVER_K ? 0 : P_BYTES) + (size_t)STAGES * TMA_STAGE_BYTES + 64 + ((size_t)table_entries + 2) * sizeof(int);
+  return 1024 + Q_BYTES + (P_OVER_K ? 0 : P_BYTES) + (size_t)STAGES * TMA_STAGE_BYTES + 128 + ((size_t)table_entries + 2) * sizeof(int);
 }
 
 }  // namespace tc

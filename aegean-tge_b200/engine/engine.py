@@ -39,7 +39,11 @@ from .runner import ModelRunner
 from .scheduler import Request, Scheduler
 
 DEFAULT_CONTEXT = 4096      # the reference's default KV length (src/models/qwen2.cpp:25)
-PAGE_SIZE = 16              # tokens per page (the reference's kBlockTokens, block_table.hpp:19)
+# Tokens per page.  The reference's unwired block table uses 16 (kBlockTokens, block_table.hpp:19), and 16 is
+# fully supported (``page_size=16``).  The default is 64, one attention tile: the kernels fetch K and V by TMA
+# one box per page and 64 columns, and an SM's TMA unit moves 2 KB boxes (16-token pages) at about 18 bytes per
+# clock but 8 KB boxes (64-token pages) at about 31, which is what long contexts are read at.
+PAGE_SIZE = 64
 
 
 class Engine:
@@ -58,6 +62,8 @@ class Engine:
             raise RuntimeError("this engine runs on a CUDA device only; none is available")
         if (model_dir is None) == (random_config is None):
             raise ValueError("give either model_dir or random_config")
+        if page_size <= 0 or 64 % page_size != 0:
+            raise ValueError(f"page_size {page_size} must divide 64, the attention kernels' tile of key positions")
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.dtype = parse_dtype(dtype)

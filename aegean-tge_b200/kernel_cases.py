@@ -42,7 +42,7 @@ def run_gemm(args) -> None:
 
 def run_attention(args) -> None:
     dev = "cuda:0"
-    heads, kv_heads, head_dim, page = args.heads, args.kv_heads, args.head_dim, 16
+    heads, kv_heads, head_dim, page = args.heads, args.kv_heads, args.head_dim, args.page_size
     batch, context, q_len = args.batch, args.context, args.q_len
     pages_per = -(-context // page)
     num_pages = batch * pages_per + 1
@@ -55,19 +55,23 @@ def run_attention(args) -> None:
     q_start = (torch.arange(batch + 1, device=dev, dtype=torch.int32) * q_len).contiguous()
     start_pos = torch.full((batch,), start_position, device=dev, dtype=torch.int32)
     q = torch.randn(batch * q_len, heads * head_dim, device=dev, dtype=torch.bfloat16)
-    times = []
+    positions = positions.contiguous()
+    run = lambda: ops.attention(q, k, v, table, q_start, start_pos, positions, seq_of, batch, q_len, context, heads,
+                                kv_heads, head_dim, 1.0 / math.sqrt(head_dim))
+    for _ in range(3):
+        run()
+    # launches queued back to back between two events: the device time of one, without the host's launch cost
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
     for _ in range(args.repeat):
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        ops.attention(q, k, v, table, q_start, start_pos, positions.contiguous(), seq_of, batch, q_len, context, heads,
-                      kv_heads, head_dim, 1.0 / math.sqrt(head_dim))
-        stop.record()
-        torch.cuda.synchronize()
-        times.append(start.elapsed_time(stop) * 1e3)
-    us = sorted(times[2:])[len(times[2:]) // 2]
+        run()
+    stop.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(stop) * 1e3 / args.repeat
     kv_bytes = batch * context * kv_heads * head_dim * 2 * 2
     flops = 4.0 * heads * head_dim * batch * q_len * (start_position + (q_len + 1) / 2.0)
-    print(f"attention batch={batch} context={context} q_len={q_len}: {us:.1f} us (with launch), "
+    print(f"attention batch={batch} context={context} q_len={q_len}: {us:.1f} us (pages of {page}), "
           f"K/V {kv_bytes / 1e6:.1f} MB at {kv_bytes / us / 1e3:.0f} GB/s, {flops / us / 1e6:.1f} TFLOP/s")
 
 
@@ -87,6 +91,7 @@ def main(argv=None) -> int:
     attn.add_argument("--heads", type=int, default=28)
     attn.add_argument("--kv-heads", type=int, default=4)
     attn.add_argument("--head-dim", type=int, default=128)
+    attn.add_argument("--page-size", type=int, default=16)
     attn.add_argument("--repeat", type=int, default=8)
     args = parser.parse_args(argv)
     if args.what == "gemm":

@@ -70,4 +70,4 @@ def test_info_json_needs_no_gpu():
     out = _run("info", "--json")
     assert out.returncode == 0
     facts = json.loads(out.stdout)
-    assert facts["kernel_target"] == "sm_100a" and facts["page_size"] == 16
+    assert facts["kernel_target"] == "sm_100a" and facts["page_size"] == 64

@@ -82,10 +82,11 @@ def test_last_32_tokens_one_by_one(model_dirs, oracle, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", MODELS)
-def test_portions_of_changing_size(model_dirs, oracle, name, dtype):
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_portions_of_changing_size(model_dirs, oracle, name, dtype, page_size):
     tokens = _tokens(name, 120, salt=2)
     ref = oracle(name, tokens)
-    engine = _engine(model_dirs, name, dtype)
+    engine = _engine(model_dirs, name, dtype, page_size=page_size)
     cuts = [7, 2, 16, 3, 2, 30, 2, 17, 41]
     assert sum(cuts) == len(tokens)
     rows, pos = [], 0
@@ -97,12 +98,15 @@ def test_portions_of_changing_size(model_dirs, oracle, name, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", MODELS)
-def test_mixed_batches_with_page_reuse(model_dirs, oracle, name, dtype):
+@pytest.mark.parametrize("page_size,pool_tokens", [(16, 320), (64, 512), (32, 384)])
+def test_mixed_batches_with_page_reuse(model_dirs, oracle, name, dtype, page_size, pool_tokens):
     """Up to four live requests, prompt portions beside decoded tokens, so few pages that they are reused."""
     from aegean_tge_b200 import ops
     lengths = {"a": 70, "b": 45, "c": 130, "d": 19, "e": 64, "f": 33}
     tokens = {r: _tokens(name, n, salt=ord(r)) for r, n in lengths.items()}
-    engine = _engine(model_dirs, name, dtype, max_tokens=320)       # 20 pages: a+b+c+d alone need 18
+    # pages of 16: 20 pages, a+b+c+d alone need 18; of 64: 8 pages for 7; of 32: 12 pages for 11
+    engine = _engine(model_dirs, name, dtype, max_tokens=pool_tokens, page_size=page_size)
+    seen_pages = set()
     got = {r: [] for r in lengths}
     done = {r: 0 for r in lengths}
 
@@ -116,6 +120,7 @@ def test_mixed_batches_with_page_reuse(model_dirs, oracle, name, dtype):
             got[r].append(logits[row:row + count])
             row += count
             done[r] += count
+            seen_pages.update(x for x in engine.cache.groups[0].tables[r] if x >= 0)
             if done[r] == lengths[r]:
                 engine.runner.finish(r)
         engine.cache.check()
@@ -130,6 +135,8 @@ def test_mixed_batches_with_page_reuse(model_dirs, oracle, name, dtype):
     run([("f", 1), ("e", 1)])
     run([("e", 44), ("f", 2)])
     assert all(done[r] == lengths[r] for r in lengths)
+    total_pages = sum(-(-n // page_size) for n in lengths.values())
+    assert len(seen_pages) <= engine.cache.groups[0].pool.capacity < total_pages       # pages were used again
     for r in lengths:
         assert rel_error(torch.cat(got[r]), oracle(name, tokens[r])) < MODEL_TOL[dtype], r
     ops.check_status()
@@ -138,12 +145,13 @@ def test_mixed_batches_with_page_reuse(model_dirs, oracle, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding(model_dirs, oracle, dtype):
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_long_decoding(model_dirs, oracle, dtype, page_size):
     """A short prompt, then 200 tokens one by one (teacher-forced), across many page edges."""
     name = "B"
     tokens = _tokens(name, 210, salt=3)
     ref = oracle(name, tokens)
-    engine = _engine(model_dirs, name, dtype)
+    engine = _engine(model_dirs, name, dtype, page_size=page_size)
     rows = [engine.runner.step([_portion("r", tokens[:10])])]
     for t in range(10, 210):
         rows.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
@@ -203,7 +211,10 @@ def test_generation_does_not_depend_on_pages_or_budget(model_dirs):
     params = [SamplingParams(temperature=0.8, seed=11 + i) for i in range(4)]
     outputs = []
     for kw in (dict(max_tokens=2048, max_batch_tokens=512), dict(max_tokens=2048, max_batch_tokens=16, chunk=16),
-               dict(num_pages=15, max_batch_tokens=16, chunk=16), dict(num_pages=13, max_batch_tokens=40, chunk=7)):
+               dict(num_pages=15, page_size=16, max_batch_tokens=16, chunk=16),
+               dict(num_pages=13, page_size=16, max_batch_tokens=40, chunk=7),
+               dict(num_pages=5, page_size=64, max_batch_tokens=40, chunk=24),
+               dict(num_pages=7, page_size=32, max_batch_tokens=16)):
         engine = Engine(model_dirs[name], dtype="float32", context=256, max_requests=4, **kw)
         outputs.append(engine.generate(prompts, n=24, sampling=params))
         engine.cache.check()
@@ -275,7 +286,7 @@ def test_bench_continuous_transcripts_are_identical(model_dirs, capsys):
     from aegean_tge_b200.cli import main
     code = main(["bench", "continuous", "--model", model_dirs["B"], "--dtype", "float32", "--requests", "7",
                  "--sequences", "3", "--tokens", "12", "--prompt-tokens", "21", "--context", "128", "--num-pages", "9",
-                 "--max-batch-tokens", "16"])
+                 "--page-size", "16", "--max-batch-tokens", "16"])
     out = capsys.readouterr().out
     assert code == 0, out
     assert "independent (all transcripts identical)" in out and "7 requests, 3 slots" in out
