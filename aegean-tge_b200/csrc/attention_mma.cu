@@ -1329,7 +1329,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
         configured_tc = smem;
       }
       const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;
-      dim3 grid(tiles, kv_heads, num_splits);
+      dim3 grid(tiles * kv_heads, 1, num_splits);
       tge_launch(tc::attention_prefill_tc_kernel, grid, tc::THREADS, smem, stream, *map_k, *map_v, p);
       int rc = tge_check_launch("attention_prefill_tc");
       if (rc != 0) return rc;

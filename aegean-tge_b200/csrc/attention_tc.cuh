@@ -128,12 +128,15 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   int* local_table = reinterpret_cast<int*>(generic + (stages - base) + STAGES * TMA_STAGE_BYTES + 128);   // after the barriers
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int kvh = blockIdx.y, split = blockIdx.z;
+  // Blocks are handed out in the order of blockIdx.x: the kv head changes fastest, so that the long tiles of
+  // every kv head start first and the short ones fill the gaps (with the kv head as blockIdx.y, a whole kv
+  // head's long tiles started only after the first ones' short tiles).
+  const int kvh = (int)blockIdx.x % p.kv_heads, tile_rank = (int)blockIdx.x / p.kv_heads, split = blockIdx.z;
   pdl_wait();
   if (tid == 0) {
     int total = 0;
     for (int s = 0; s < p.num_seqs; ++s) total += (p.q_start[s + 1] - p.q_start[s] + p.bq - 1) / p.bq;
-    int remaining = total - 1 - (int)blockIdx.x, seq = -1, tile = 0;          // long tiles first
+    int remaining = total - 1 - tile_rank, seq = -1, tile = 0;                // long tiles first
     for (int s = 0; s < p.num_seqs && remaining >= 0; ++s) {
       const int tiles = (p.q_start[s + 1] - p.q_start[s] + p.bq - 1) / p.bq;
       if (remaining < tiles) { seq = s; tile = remaining; break; }
