@@ -57,7 +57,7 @@ def run_attention(args) -> None:
     q = torch.randn(batch * q_len, heads * head_dim, device=dev, dtype=torch.bfloat16)
     positions = positions.contiguous()
     run = lambda: ops.attention(q, k, v, table, q_start, start_pos, positions, seq_of, batch, q_len, context, heads,
-                                kv_heads, head_dim, 1.0 / math.sqrt(head_dim))
+                                kv_heads, head_dim, 1.0 / math.sqrt(head_dim), split_tokens=args.split)
     for _ in range(3):
         run()
     # launches queued back to back between two events: the device time of one, without the host's launch cost
@@ -91,7 +91,8 @@ def main(argv=None) -> int:
     attn.add_argument("--heads", type=int, default=28)
     attn.add_argument("--kv-heads", type=int, default=4)
     attn.add_argument("--head-dim", type=int, default=128)
-    attn.add_argument("--page-size", type=int, default=16)
+    attn.add_argument("--page-size", type=int, default=64)
+    attn.add_argument("--split", type=int, default=0, help="keys per split (a multiple of 64); 0 lets the wrapper choose")
     attn.add_argument("--repeat", type=int, default=8)
     args = parser.parse_args(argv)
     if args.what == "gemm":
