@@ -5,6 +5,7 @@
     tge generate --model DIR --tokens "a b c" [--n N] [--temp T] [--top-k N] [--top-p P] [--min-p P]
                  [--repeat-penalty R] [--penalty-window N] [--seed N] [--context N] [--print-ids]
     tge bench prefill|decode --model DIR [--prompt-len N] [--batch B] [--n N] [--repeat R]
+    tge fidelity --model DIR [--context N] [--tokens N] [--corpus FILE]
     tge bench continuous --model DIR [--requests N] [--tokens N] [--sequences N] [--prompt-tokens N] [--prompt-max N]
     tge make-random --config FILE --out DIR [--seed S] [--dtype float32|bfloat16]
     tge replay --model DIR --dtype D --out DIR --max-tokens N          (same as bin/trace_run)
@@ -96,6 +97,10 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--sequences", type=int, default=4, help="continuous: requests live at a time (default 4)")
     bench.add_argument("--prompt-tokens", type=int, default=1, help="continuous: prompt length (default 1)")
     bench.add_argument("--prompt-max", type=int, help="continuous: draw each prompt's length from [prompt-tokens, this]")
+    fidelity = commands.add_parser("fidelity", help="the float32 path against the bfloat16 kernels, teacher-forced")
+    _model_args(fidelity)
+    fidelity.add_argument("--corpus", help="file of token ids separated by white space (default: seeded random ids)")
+    fidelity.add_argument("--tokens", type=int, default=256, help="positions to compare (default 256)")
     make = commands.add_parser("make-random", help="write a model folder with seeded random weights")
     make.add_argument("--config", required=True, help="a config.json")
     make.add_argument("--out", required=True)
@@ -246,6 +251,68 @@ def command_generate(args) -> int:
     return 0
 
 
+def command_fidelity(args) -> int:
+    """The reference's ``fidelity`` (apps/cli/main.cpp:2379-2596) runs its full-scalar oracle and the selected
+    kernels over the same tokens, teacher-forced, and reports KL, the largest logit difference and top-1
+    agreement.  Here the oracle is the engine's own true 32-bit path and the candidate its bfloat16 kernels;
+    the first half of the tokens runs as one prompt, the second half one token at a time."""
+    import gc
+    import random
+    import time
+    import torch
+    from .engine.batch import Portion
+    if args.tokens < 2:
+        raise UsageError("fidelity: at least two tokens")
+    started = time.time()
+    logits = {}
+    tokens = None
+    load_seconds = 0.0
+    for dtype in ("float32", "bfloat16"):
+        args.dtype = dtype
+        args.max_requests = 1
+        t0 = time.time()
+        engine = _engine_from(args)
+        load_seconds += time.time() - t0
+        if tokens is None:
+            vocab = engine.spec.vocab_size
+            if args.corpus:
+                with open(args.corpus, "r", encoding="utf-8") as handle:
+                    tokens = [int(t) for t in handle.read().split()]
+                if any(not 0 <= t < vocab for t in tokens):
+                    raise UsageError(f"fidelity: the corpus holds ids outside the vocabulary of {vocab}")
+            else:
+                rnd = random.Random(4321)
+                tokens = [rnd.randrange(vocab) for _ in range(args.tokens)]
+            tokens = tokens[:min(args.tokens, engine.max_model_len)]
+            if len(tokens) < 2:
+                raise UsageError(f"fidelity: corpus needs two tokens within the {engine.max_model_len}-token context")
+        half = max(len(tokens) // 2, 1)
+        rows = [engine.runner.step([Portion("f", tokens[:half], list(range(half)))]).double()]
+        for t in range(half, len(tokens)):
+            rows.append(engine.runner.step([Portion("f", tokens[t:t + 1], [0])]).double())
+        logits[dtype] = torch.cat(rows)
+        from . import ops
+        ops.check_status()
+        del engine, rows
+        gc.collect()
+        torch.cuda.empty_cache()
+    reference, candidate = logits["float32"], logits["bfloat16"]
+    log_p = torch.log_softmax(reference, dim=-1)
+    log_q = torch.log_softmax(candidate, dim=-1)
+    kl = (log_p.exp() * (log_p - log_q)).sum(-1)
+    agree = int((reference.argmax(-1) == candidate.argmax(-1)).sum())
+    positions = reference.shape[0]
+    print("fidelity : float32 path vs bfloat16 kernels (prompt of %d tokens, then %d single tokens)"
+          % (max(len(tokens) // 2, 1), positions - max(len(tokens) // 2, 1)))
+    print(f"load     : {load_seconds * 1e3:.1f} ms")
+    print(f"corpus   : {positions} positions")
+    print(f"KL       : mean {float(kl.mean()):.3e}, worst {float(kl.max()):.3e} nats")
+    print(f"logits   : max |diff| {float((reference - candidate).abs().max()):.3e} (largest |logit| {float(reference.abs().max()):.3e})")
+    print(f"top-1    : {agree}/{positions} agree")
+    print(f"time     : {time.time() - started:.2f} s")
+    return 0
+
+
 def command_bench_continuous(args) -> int:
     """Continuous batching as the reference's ``bench continuous`` runs it (apps/cli/main.cpp:1451-1644):
     ``requests`` requests through ``sequences`` live slots, greedy, ``tokens`` new tokens each.  With one
@@ -355,6 +422,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             return command_generate(args)
         if args.command == "bench":
             return command_bench(args)
+        if args.command == "fidelity":
+            return command_fidelity(args)
         if args.command == "make-random":
             return command_make_random(args)
         if args.command == "replay":

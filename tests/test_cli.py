@@ -42,6 +42,7 @@ def test_usage_errors_exit_with_2():
     assert _run("generate", "--model", "x", "--n", "0").returncode == 2
     assert _run("generate", "--model", "x", "--top-p", "1.5", "--tokens", "1 2").returncode == 2
     assert _run("bench", "sideways").returncode == 2
+    assert _run("fidelity", "--model", "x", "--tokens", "1").returncode == 2
     assert _run("bench", "continuous", "--model", "x", "--requests", "0").returncode == 2
     assert _run("bench", "continuous", "--model", "x", "--prompt-tokens", "9", "--prompt-max", "3").returncode == 2
     assert _run("replay", "--model", "x").returncode == 2

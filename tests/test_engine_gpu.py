@@ -293,3 +293,14 @@ def test_bench_continuous_transcripts_are_identical(model_dirs, capsys):
     code = main(["bench", "continuous", "--model", model_dirs["A"], "--requests", "5", "--sequences", "2", "--tokens", "6",
                  "--prompt-tokens", "3", "--prompt-max", "40", "--context", "128"])
     assert code == 0 and "not compared" in capsys.readouterr().out
+
+
+def test_fidelity_of_the_bfloat16_kernels(model_dirs, capsys):
+    """`tge fidelity`: the float32 path as oracle, the bfloat16 kernels as candidate, teacher-forced."""
+    import re
+    from aegean_tge_b200.cli import main
+    assert main(["fidelity", "--model", model_dirs["B"], "--tokens", "90", "--context", "128"]) == 0
+    out = capsys.readouterr().out
+    mean_kl = float(re.search(r"KL       : mean ([0-9.e+-]+)", out).group(1))
+    agree, total = map(int, re.search(r"top-1    : (\d+)/(\d+) agree", out).groups())
+    assert total == 90 and mean_kl < 1e-3 and agree >= 80, out
