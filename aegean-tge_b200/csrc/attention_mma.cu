@@ -1105,6 +1105,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
 }
 
 #include "attention_tc.cuh"
+#include "attention_tc2.cuh"
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1317,7 +1318,34 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     static const bool use_tc = getenv("TGE_NO_TC_ATTENTION") == nullptr || getenv("TGE_NO_TC_ATTENTION")[0] == '\0';
     if (use_tc && tc::smem_bytes(range >> p.page_shift) <= 227 * 1024 && q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 &&
         out_stride % 8 == 0 && (uintptr_t)out % 16 == 0) {
-      // the tcgen05 kernel: 128 rows per block as well
+      // the tcgen05 kernels: 128 rows per query tile as well
+      static const bool one_tile = getenv("TGE_ATTENTION_ONE_TILE") != nullptr && getenv("TGE_ATTENTION_ONE_TILE")[0] != '\0';
+      if (tc2::FITS && !one_tile && tc2::smem_bytes(range >> p.page_shift) <= 227 * 1024) {
+        // two query tiles per block, one block per SM
+        const size_t smem2 = tc2::smem_bytes(range >> p.page_shift);
+        static size_t configured_tc2 = 0;
+        if (smem2 > configured_tc2) {
+          cudaError_t err = cudaFuncSetAttribute(tc2::attention_prefill_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+          if (err != cudaSuccess) {
+            tge_set_error("attention_prefill_tc2: cannot reserve %zu bytes of shared memory: %s", smem2, cudaGetErrorString(err));
+            return -2;
+          }
+          configured_tc2 = smem2;
+        }
+        const int pairs = ((tokens + p.bq - 1) / p.bq + 1) / 2 + num_seqs;
+        dim3 grid2(pairs * kv_heads, 1, num_splits);
+        tge_launch(tc2::attention_prefill_tc2_kernel, grid2, tc2::THREADS, smem2, stream, *map_k, *map_v, p);
+        int rc2 = tge_check_launch("attention_prefill_tc2");
+        if (rc2 != 0) return rc2;
+        if (num_splits > 1) {
+          dim3 mgrid(tokens, heads);
+          tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
+                     (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
+                     window, p.split_tokens, num_splits);
+          return tge_launched("attention_merge", 2);
+        }
+        return 1;
+      }
       const size_t smem = tc::smem_bytes(range >> p.page_shift);
       static size_t configured_tc = 0;
       if (smem > configured_tc) {

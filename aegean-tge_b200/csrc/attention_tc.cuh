@@ -309,7 +309,8 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
       load32(s_now + lane_base + 32, s_bits + 32);
       wait_loads();
       // a tile that every row of the warp sees whole needs no mask
-      const bool whole = row_valid && k0 + BKV - 1 <= row_pos && k0 >= first_key && k0 >= lo && k0 + BKV <= hi;
+      // (rows beyond the tile's queries hold zeros and are never stored: they need none either)
+      const bool whole = !row_valid || (k0 + BKV - 1 <= row_pos && k0 >= first_key && k0 >= lo && k0 + BKV <= hi);
       float mx = -INFINITY;
       if (__all_sync(0xffffffffu, whole)) {
 #pragma unroll

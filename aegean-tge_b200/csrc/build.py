@@ -31,7 +31,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 CORE_SOURCES = ["host_util.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu", "sampling.cu", "sampling_cuts.cu",
                 "gemm_static_scratch.cu"]
-HEADERS = ["common.cuh", "gemm_static_scratch.h", "attention_tc.cuh"]
+HEADERS = ["common.cuh", "gemm_static_scratch.h", "attention_tc.cuh", "attention_tc2.cuh"]
 RUNTIME_SOURCES = ["runtime.cpp"]
 RUNTIME_HEADERS = ["runtime.h"]
 
