@@ -25,6 +25,7 @@ from typing import Any, Dict, Hashable, List, Optional, Sequence, Union
 import torch
 
 from .. import ops as _ops
+from .. import runtime as _rt
 from ..cache.manager import CacheManager
 from ..config.qwen2 import ConfigError, read_config_json
 from ..models.decoder import DecoderModel
@@ -171,7 +172,7 @@ class Engine:
                          "window": g.spec.window} for g in self.cache.groups]
         out["runner_steps"] = self.runner.steps
         out["runner_tokens"] = self.runner.tokens_run
-        out["libraries"] = list(_ops.loaded_libraries())
+        out["libraries"] = list(_ops.loaded_libraries()) + [_rt.library_path()]
         return out
 
     def describe(self) -> Dict[str, Any]:
