@@ -33,9 +33,9 @@ BATCH = 8
 
 def reference_arm() -> int:
     """The reference is a C++/CMake CPU engine for Windows with no Python packaging: it cannot be
-    installed with pip, has no CUDA path, and never ran this model; see DESIGN.md."""
+    installed with pip, has no CUDA path, and never ran this model."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = ("the reference is a CMake C++ CPU engine without setup.py/pyproject.toml: 'pip install /root/reference' "
+    why = ("the reference is a CMake C++ CPU engine without setup.py/pyproject.toml: 'pip install' of its source tree "
            "finds nothing to build, and it has no GPU path or bf16 model to run this metric with")
     if os.path.isdir(ref) and os.listdir(ref):
         why = "baseline/_ref holds no importable package that exposes the reference's generate path; " + why

@@ -17,7 +17,7 @@ What it does, on the CPU, touching nothing outside a temporary folder:
 
 tests/test_plain_vs_golden.py then checks the plain implementation against these files.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference PATH_TO_THE_REFERENCE_CHECKOUT
 """
 import argparse
 import hashlib
@@ -122,7 +122,7 @@ def weights_hash(weights):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of the reference engine (read only)")
     args = parser.parse_args()
     import torch
     from aegean_tge_b200 import write_random_model
