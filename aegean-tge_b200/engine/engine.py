@@ -52,7 +52,7 @@ class Engine:
                  max_tokens: Optional[int] = None, num_pages: Optional[int] = None, max_batch_tokens: int = 2048,
                  max_requests: int = 64, chunk: Optional[int] = None, device: str = "cuda:0",
                  memory_fraction: float = 0.9, random_config: Optional[Dict[str, Any]] = None, seed: int = 0,
-                 page_size: int = PAGE_SIZE):
+                 page_size: int = PAGE_SIZE, run_ahead: bool = True):
         """``model_dir``: folder with config.json and model.safetensors.  Alternatively
         ``random_config`` (a config.json as a dict) and ``seed``: random weights drawn on the device.
 
@@ -112,6 +112,10 @@ class Engine:
         self.sampler = Sampler(_ops, self.device)
         self._next_id = 0
         self.d2h_bytes_last = 0
+        self.run_ahead = run_ahead
+        self._ahead = None
+        self.ahead_used = 0
+        self.ahead_dropped = 0
 
     # -- requests -------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], n: int = 32, sampling: Optional[SamplingParams] = None,
@@ -130,18 +134,91 @@ class Engine:
         return self.scheduler.has_work()
 
     def step(self) -> List[Request]:
-        """Plans one step, runs it, samples, and returns the requests that finished in it."""
+        """Plans one step, runs it, samples, and returns the requests that finished in it.
+
+        While every live request is decoding with a sampler that stays on the device, the next step is
+        queued before this step's tokens are read (its token ids are taken from the device), so the GPU
+        does not wait for the host between steps.  The step queued ahead is used only if the scheduler
+        then plans exactly that step; otherwise (a request ended on an end token, a new one arrived, pages
+        ran out) its results are dropped, the generators it drew from are put back, and the planned step
+        runs as usual.  What it wrote into the cache lies beyond every request's recorded length.
+        """
         plan = self.scheduler.schedule()
-        logits = self.runner.step_plan(plan)
+        ahead, self._ahead = self._ahead, None
+        pending = None
+        if ahead is not None:
+            if self._matches(ahead, plan):
+                pending = ahead["result"]
+                self.ahead_used += 1
+            else:
+                for request, state in zip(ahead["requests"], ahead["rng_states"]):
+                    request.rng.state = state
+                self.ahead_dropped += 1
         sampling_items = [item for item in plan.items if item.samples]
-        sampled: List[int] = []
-        if sampling_items:
-            sampled = self.sampler.sample(logits, [item.request.sampling for item in sampling_items],
-                                          [item.request.rng for item in sampling_items],
-                                          [item.request.tokens if item.request.sampling.has_penalty else ()
-                                           for item in sampling_items])
-            self.d2h_bytes_last = 4 * len(sampled)
+        if pending is None:
+            logits = self.runner.step_plan(plan)
+            if sampling_items:
+                params = [item.request.sampling for item in sampling_items]
+                if self.run_ahead and Sampler.stays_on_device(params):
+                    pending = self.sampler.sample_async(logits, params, [item.request.rng for item in sampling_items])
+                else:
+                    sampled = self.sampler.sample(logits, params, [item.request.rng for item in sampling_items],
+                                                  [item.request.tokens if item.request.sampling.has_penalty else ()
+                                                   for item in sampling_items])
+                    self.d2h_bytes_last = 4 * len(sampled)
+                    return self.scheduler.update(plan, sampled)
+            else:
+                return self.scheduler.update(plan, [])
+        ids, host, event = pending
+        if self._may_run_ahead(plan):
+            self._ahead = self._launch_ahead(plan, ids)
+        event.synchronize()
+        sampled = host.tolist()
+        self.d2h_bytes_last = 4 * len(sampled)
         return self.scheduler.update(plan, sampled)
+
+    # -- the step queued ahead ----------------------------------------------------
+    def _may_run_ahead(self, plan) -> bool:
+        items = plan.items
+        if not self.run_ahead or not items or not self.runner.can_step_ahead(len(items)):
+            return False
+        if self.scheduler.num_waiting():
+            return False
+        for item in items:
+            request = item.request
+            if item.count != 1 or not item.samples:
+                return False
+            # the token this step draws must not be the request's last, and must leave room for one more
+            if len(request.output) + 1 >= request.max_new_tokens or request.num_tokens + 2 > self.max_model_len:
+                return False
+        return Sampler.stays_on_device([item.request.sampling for item in items])
+
+    def _launch_ahead(self, plan, ids: torch.Tensor):
+        """Queues the step after ``plan`` for the same requests, fed with ``ids`` from the device."""
+        from ..cache.pages import PoolExhausted
+        requests = [item.request for item in plan.items]
+        names = [r.id for r in requests]
+        # this step's tokens are computed as far as the cache is concerned (the scheduler records the same later)
+        for item in plan.items:
+            self.cache.set_computed(item.request.id, item.start + item.count)
+        states = [r.rng.state for r in requests]
+        try:
+            logits = self.runner.step_ahead(names, ids)
+        except PoolExhausted:
+            return None
+        result = self.sampler.sample_async(logits, [r.sampling for r in requests], [r.rng for r in requests])
+        return {"requests": requests, "starts": [item.start + 1 for item in plan.items], "rng_states": states,
+                "result": result}
+
+    @staticmethod
+    def _matches(ahead, plan) -> bool:
+        items = plan.items
+        if len(items) != len(ahead["requests"]):
+            return False
+        for item, request, start in zip(items, ahead["requests"], ahead["starts"]):
+            if item.request is not request or item.start != start or item.count != 1 or not item.samples:
+                return False
+        return True
 
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], n: int = 32,
                  sampling: Union[None, SamplingParams, Sequence[SamplingParams]] = None) -> Union[List[int], List[List[int]]]:
@@ -170,6 +247,7 @@ class Engine:
         out = dict(self.scheduler.counters)
         out["pages"] = [{"capacity": g.pool.capacity, "free": g.pool.free_count, "layers": len(g.layers),
                          "window": g.spec.window} for g in self.cache.groups]
+        out["steps_queued_ahead"] = {"used": self.ahead_used, "dropped": self.ahead_dropped}
         out["runner_steps"] = self.runner.steps
         out["runner_tokens"] = self.runner.tokens_run
         out["libraries"] = list(_ops.loaded_libraries()) + [_rt.library_path()]

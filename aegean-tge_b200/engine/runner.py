@@ -137,8 +137,36 @@ class ModelRunner:
         return self._run(lambda width, pad_rows, out, layout: plan.pack(vocab, width, pad_rows, out, layout),
                          len(items), tokens, single, max_ctx, wanted, None)
 
+    def can_step_ahead(self, batch: int) -> bool:
+        return self.use_graphs and batch <= self.max_graph_batch
+
+    def step_ahead(self, requests: Sequence[Hashable], token_ids: torch.Tensor) -> torch.Tensor:
+        """One more token for each of ``requests`` (each already advanced past its previous step), the
+        token ids taken from ``token_ids`` on the device: the step can be queued before the host has seen them.
+
+        Pages are reserved all or nothing (PoolExhausted if they do not fit); progress is not recorded.
+        Returns the logits of every row.
+        """
+        cache, lib = self.cache, self._lib
+        count = len(requests)
+        handles = (ctypes.c_int64 * count)(*[cache.handle_of(r) for r in requests])
+        dummy = np.zeros(count, dtype=np.int32)
+        want = np.zeros(count, dtype=np.int32)
+        token_ptrs = (ctypes.c_void_p * count)(*[dummy.ctypes.data + 4 * i for i in range(count)])
+        want_ptrs = (ctypes.c_void_p * count)(*[want.ctypes.data + 4 * i for i in range(count)])
+        ones = (ctypes.c_int * count)(*([1] * count))
+        vocab = self.model.spec.vocab_size
+
+        def pack(width: int, pad_rows: int, out: np.ndarray, layout) -> int:
+            return _rt.check(lib.tge_rt_step_pack(cache.native, count, handles, token_ptrs, ones, want_ptrs, ones, vocab,
+                                                  self.max_model_len, width, pad_rows, out.ctypes.data, out.size,
+                                                  ctypes.byref(layout)))
+
+        max_ctx = lib.tge_rt_cache_max_context(cache.native, handles, ones, count)
+        return self._run(pack, count, count, True, max_ctx, list(range(count)), None, device_tokens=token_ids)
+
     def _run(self, pack: Packer, batch: int, tokens: int, single: bool, max_ctx: int, wanted: List[int],
-             packed: Optional[Callable[[], None]]) -> Optional[torch.Tensor]:
+             packed: Optional[Callable[[], None]], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         groups = len(self.cache.groups)
         if self.use_graphs and single and batch <= self.max_graph_batch:
             bound = 1024
@@ -148,7 +176,7 @@ class ModelRunner:
             graph = self._graphs.get((batch, bound))
             if graph is None:
                 graph = self._graphs[(batch, bound)] = DecodeGraph(self, batch, bound)
-            logits = graph.run(pack, packed)
+            logits = graph.run(pack, packed, device_tokens)
             self.ops.launches += graph.kernels
             self.h2d_bytes_last = graph.nbytes
             self.graph_replays += 1
@@ -236,7 +264,8 @@ class DecodeGraph:
         self.kernels = ops.launches - before
         ops.launches = before
 
-    def run(self, pack: Packer, packed: Optional[Callable[[], None]]) -> torch.Tensor:
+    def run(self, pack: Packer, packed: Optional[Callable[[], None]],
+            device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         staging = self.staging
         turn = staging.take()
         layout = _rt.StepLayout()
@@ -247,5 +276,7 @@ class DecodeGraph:
             packed()
         self.dev.copy_(staging.hosts[turn], non_blocking=True)
         staging.queued(turn)
+        if device_tokens is not None:      # the token ids are still on the device: they overwrite the packed placeholders
+            self.dev[self.layout.token_ids:self.layout.token_ids + self.batch].copy_(device_tokens, non_blocking=True)
         self.graph.replay()
         return self.logits

@@ -212,6 +212,9 @@ class Scheduler:
         self._requests[request.id] = request
         self.finished.pop(request.id, None)
 
+    def num_waiting(self) -> int:
+        return int(self._lib.tge_rt_sched_waiting(self._native, self._ids, 0))
+
     def has_work(self) -> bool:
         return bool(self._lib.tge_rt_sched_has_work(self._native))
 

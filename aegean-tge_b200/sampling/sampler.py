@@ -24,12 +24,40 @@ class Sampler:
         self.ops = ops
         self.device = device
         self._zeros = {}            # rows -> float32 zeros [2, rows] on the device (greedy: temperature 0, no draw)
+        self._pinned = {}           # rows -> ring of pinned int32 buffers for ids on their way to the host
 
     def _to_device(self, values, dtype) -> torch.Tensor:
         host = torch.tensor(values, dtype=dtype)
         if self.device.type == "cuda":
             host = host.pin_memory()
         return host.to(self.device, non_blocking=True)
+
+    @staticmethod
+    def stays_on_device(params: Sequence[SamplingParams]) -> bool:
+        """True when every row is greedy or a plain temperature draw: no history, no sort, one kernel."""
+        return all(not p.has_penalty and (p.greedy or not p.has_cuts) for p in params)
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[XorShift32]):
+        """Like :meth:`sample` for rows that stay on the device, without waiting: returns the ids on the
+        device, their copy in pinned host memory, and the event after which that copy is complete."""
+        rows = logits.shape[0]
+        if all(p.greedy for p in params):
+            if rows not in self._zeros:
+                self._zeros[rows] = torch.zeros((2, rows), dtype=torch.float32, device=self.device)
+            floats = self._zeros[rows]
+        else:
+            floats = self._to_device([[max(float(p.temperature), 0.0) for p in params],
+                                      [0.0 if p.greedy else rng.next_uniform() for p, rng in zip(params, rngs)]],
+                                     torch.float32)
+        ids = self.ops.sample(logits, floats[0], floats[1])
+        turn = self._turn = (getattr(self, "_turn", -1) + 1) % 4
+        if rows not in self._pinned:
+            self._pinned[rows] = [torch.empty(rows, dtype=torch.int32).pin_memory() for _ in range(4)]
+        host = self._pinned[rows][turn]
+        host.copy_(ids, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return ids, host, event
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[XorShift32],
                histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:

@@ -172,7 +172,8 @@ def main() -> int:
         },
         "clocks": clocks,
         "e2e": {"value": round(BATCH * args.steps / e2e_seconds, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps_queued_ahead": engine.stats()["steps_queued_ahead"]["used"]},
         "gpu_launches": main_run["launches"],
         "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
                     "frac": round(prefill["frac"], 4)},

@@ -304,3 +304,40 @@ def test_fidelity_of_the_bfloat16_kernels(model_dirs, capsys):
     mean_kl = float(re.search(r"KL       : mean ([0-9.e+-]+)", out).group(1))
     agree, total = map(int, re.search(r"top-1    : (\d+)/(\d+) agree", out).groups())
     assert total == 90 and mean_kl < 1e-3 and agree >= 80, out
+
+
+def test_steps_queued_ahead_change_nothing(model_dirs, tmp_path):
+    """Decode steps are queued before the previous step's tokens are read.  With and without that the same
+    tokens come out: greedy and temperature rows, requests of different lengths, and a request that ends on an
+    end token (the step queued for it is dropped and its generator put back)."""
+    import json
+    import shutil
+    from aegean_tge_b200 import Engine, SamplingParams
+    prompts = [_tokens("A", n, salt=90 + n) for n in (9, 30, 17)]
+    params = [SamplingParams(temperature=0.9, seed=5), SamplingParams(), SamplingParams(temperature=0.7, seed=6)]
+
+    def run(folder, run_ahead):
+        engine = Engine(folder, dtype="float32", context=256, max_tokens=1024, max_requests=4, run_ahead=run_ahead)
+        ids = [engine.add_request(p, n, s) for p, n, s in zip(prompts, (40, 25, 33), params)]
+        done = {}
+        while engine.has_unfinished():
+            for request in engine.step():
+                done[request.id] = request
+        engine.cache.check()
+        return [done[i].output for i in ids], [done[i].finish_reason for i in ids], engine.stats()["steps_queued_ahead"]
+
+    plain, reasons, counts = run(model_dirs["A"], False)
+    assert counts == {"used": 0, "dropped": 0} and reasons == ["length"] * 3
+    ahead, _, counts = run(model_dirs["A"], True)
+    assert ahead == plain and counts["used"] > 20
+    # the same model with an end token that the first request draws on its way
+    stop = plain[0][15]
+    folder = tmp_path / "with_end_token"
+    shutil.copytree(model_dirs["A"], folder)
+    config = json.loads((folder / "config.json").read_text())
+    config["eos_token_id"] = stop
+    (folder / "config.json").write_text(json.dumps(config))
+    plain, reasons, _ = run(str(folder), False)
+    assert "end_token" in reasons
+    ahead, reasons_ahead, counts = run(str(folder), True)
+    assert ahead == plain and reasons_ahead == reasons and counts["dropped"] >= 1 and counts["used"] > 5
