@@ -31,7 +31,7 @@ constexpr int STAGES = 2;
 constexpr int Q_BYTES = ROWS * HD * 2;
 constexpr int P_BYTES = ROWS * BKV * 2;            // 16 KiB
 constexpr bool P_OVER_K = TMA_TILE_BYTES >= P_BYTES;   // P reuses the K tile of its stage when that is large enough
-constexpr int TMEM_COLS = (2 * BKV + HD) <= 128 ? 128 : 256;        // two score buffers and the output
+constexpr int TMEM_COLS = (2 * BKV + HD) <= 128 ? 128 : ((2 * BKV + HD) <= 256 ? 256 : 512);   // two score buffers and the output, a power of two
 
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }

@@ -261,7 +261,7 @@ def test_attention_simt(ops, dtype, heads, kv_heads, head_dim):
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim", [(6, 2, 48), (3, 1, 32), (4, 4, 16), (7, 1, 128), (28, 4, 64),
-                                                     (5, 5, 80), (40, 2, 16)])
+                                                     (5, 5, 80), (40, 2, 16), (4, 2, 256), (6, 2, 192)])
 @pytest.mark.parametrize("q_lens,starts", [([5, 1, 37, 2], [30, 150, 0, 63]), ([1, 1, 1], [0, 199, 64]),
                                            ([130], [0]), ([70, 3], [200, 15])])
 def test_attention_mma(ops, heads, kv_heads, head_dim, q_lens, starts):
