@@ -44,7 +44,16 @@ TINY_D = {
     "tie_word_embeddings": False, "max_position_embeddings": 4096, "use_sliding_window": False,
     "hidden_act": "silu",
 }
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
+# tiny E: nothing is a multiple of 8 or 16 (head size 20, width 100, inner width 70, a prime vocabulary, as many
+# kv heads as query heads, tied head): what the tensor-core and 16-byte kernels refuse goes to the plain ones
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "num_hidden_layers": 2, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 20, "intermediate_size": 70, "vocab_size": 97, "rope_theta": 2000.0, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": True, "max_position_embeddings": 300, "use_sliding_window": False,
+    "hidden_act": "silu",
+}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3), "E": (TINY_E, 4)}
 
 
 def pytest_configure(config):

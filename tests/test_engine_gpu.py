@@ -10,7 +10,7 @@ from plain import qwen2_plain as plain
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-MODELS = ["A", "B", "C", "D"]
+MODELS = ["A", "B", "C", "D", "E"]
 
 
 def _tokens(name, count, salt=0):
