@@ -43,7 +43,9 @@ class _Parser(argparse.ArgumentParser):
 
 def _model_args(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--model", help="model folder (config.json + model.safetensors)")
-    parser.add_argument("--random-config", help="config.json file: run with seeded random weights instead of --model")
+    parser.add_argument("--random-config", "--config", dest="random_config",
+                        help="config.json file: run with seeded random weights instead of --model")
+    parser.add_argument("--random-weights", action="store_true", help="(implied by --random-config / --config)")
     parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights")
     parser.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     parser.add_argument("--context", type=int, default=4096, help="KV cache length (default 4096, capped by model)")
@@ -111,6 +113,7 @@ def build_parser() -> argparse.ArgumentParser:
     replay.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     replay.add_argument("--out", required=True)
     replay.add_argument("--max-tokens", type=int, required=True)
+    replay.add_argument("--trace", help="file of steps (default: standard input)")
     commands.add_parser("version", help="print the engine version")
     return parser
 
@@ -429,7 +432,7 @@ def main(argv: Optional[List[str]] = None) -> int:
         if args.command == "replay":
             from .engine.replay import main as replay_main
             return replay_main(["--model", args.model, "--dtype", args.dtype, "--out", args.out,
-                                "--max-tokens", str(args.max_tokens)])
+                                "--max-tokens", str(args.max_tokens)] + (["--trace", args.trace] if args.trace else []))
         raise UsageError(f"unknown command {args.command}")
     except SystemExit as stop:          # argparse prints --help itself and leaves through here
         return int(stop.code or 0)

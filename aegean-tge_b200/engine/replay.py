@@ -61,6 +61,7 @@ def main(argv: Optional[list] = None) -> int:
     parser.add_argument("--out", required=True, help="folder that receives <step>.f32")
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (the cache pool is made for this many)")
+    parser.add_argument("--trace", help="file of steps, one JSON object a line (default: standard input)")
     args = parser.parse_args(argv)
     if args.max_tokens <= 0:
         parser.error("--max-tokens must be positive")
@@ -69,6 +70,9 @@ def main(argv: Optional[list] = None) -> int:
     engine = Engine(args.model, dtype=args.dtype, context=args.max_tokens, max_tokens=args.max_tokens,
                     max_requests=8, max_batch_tokens=max(args.max_tokens, 1))
     print(f"[trace_run] ready: {engine.describe()}", file=sys.stderr, flush=True)
+    if args.trace:
+        with open(args.trace, "r", encoding="utf-8") as handle:
+            return run_trace(engine, handle, args.out, sys.stdout)
     return run_trace(engine, sys.stdin, args.out, sys.stdout)
 
 
