@@ -25,7 +25,6 @@
 // TGE_STATUS_WAIT_TIMEOUT in the status word, all roles leave their loops, the
 // loader waits (bounded) for its copies in flight, tensor memory is freed and
 // the kernel returns.
-#include <cooperative_groups.h>
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -576,45 +575,36 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   return 1;
 }
 
-// A cluster of NORM_CLUSTER blocks per token: block r owns a slice of the row's columns.  Each adds the
-// k-split partial sums (+ bias) into the float32 stream, the slices' sums of squares meet through
-// distributed shared memory (added in rank order), and each block writes its slice of
-// RMSNorm(row) * weight.  Eight blocks per row keep a decode step's handful of rows from running on a
-// handful of SMs.
-constexpr int NORM_CLUSTER = 8;
-constexpr int NORM_THREADS = 128;
-constexpr int NORM_PER_THREAD = 8;               // columns per thread: rows up to 8 * 128 * 8 = 8192 wide
+// One block per token adds the k-split partial sums (+ bias) into the float32 stream and writes
+// RMSNorm(row) * weight for the next product.  (Eight blocks per row as a cluster that met through
+// distributed shared memory took 8.8 us after the o projection at batch 8, two 7.5 us, one block 7 us:
+// the cluster's barriers cost more than the parallelism gave.)
+constexpr int NORM_THREADS = 1024;
+constexpr int NORM_PER_THREAD = 8;               // columns per thread: rows up to 1024 * 8 = 8192 wide
 
-__global__ void __cluster_dims__(NORM_CLUSTER, 1, 1) __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS)
 splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ stream,
                        long long ld_stream, const float* __restrict__ norm_weight, float eps,
-                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w, int splits,
-                       int slice) {
+                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w, int splits) {
   __shared__ float scratch[32];
-  __shared__ float slice_sums[NORM_CLUSTER];       // every block receives every slice's sum of squares
   pdl_trigger();
-  cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
-  // first half of a cluster barrier: its second half, below, proves that every block of the cluster is
-  // running before anyone writes into a neighbour's shared memory
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  const int rank = blockIdx.x, t = blockIdx.y;
-  const int begin = min(rank * slice, n_w), end = min(begin + slice, n_w);
+  const int t = blockIdx.x;
   const size_t plane = (size_t)m_tok * n_w;
   // constants of the model first: they do not depend on the previous kernel
   float gain[NORM_PER_THREAD], add[NORM_PER_THREAD], value[NORM_PER_THREAD];
 #pragma unroll
   for (int i = 0; i < NORM_PER_THREAD; ++i) {
-    const int n = begin + threadIdx.x + i * NORM_THREADS;
-    gain[i] = n < end ? norm_weight[n] : 0.0f;
-    add[i] = (bias && n < end) ? bias[n] : 0.0f;
+    const int n = threadIdx.x + i * NORM_THREADS;
+    gain[i] = n < n_w ? norm_weight[n] : 0.0f;
+    add[i] = (bias && n < n_w) ? bias[n] : 0.0f;
   }
   pdl_wait();
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < NORM_PER_THREAD; ++i) {
-    const int n = begin + threadIdx.x + i * NORM_THREADS;
+    const int n = threadIdx.x + i * NORM_THREADS;
     value[i] = 0.0f;
-    if (n < end) {
+    if (n < n_w) {
       const float* src = partial + (size_t)t * n_w + n;
       float acc = 0.0f;
 #pragma unroll 4
@@ -626,17 +616,11 @@ splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restric
     }
   }
   sum = block_sum(sum, scratch);
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-  if (threadIdx.x < NORM_CLUSTER) *cluster.map_shared_rank(&slice_sums[rank], threadIdx.x) = sum;
-  cluster.sync();                                  // one meeting point: after it everybody reads only its own memory
-  float total = 0.0f;
-#pragma unroll
-  for (int r = 0; r < NORM_CLUSTER; ++r) total += slice_sums[r];
-  const float scale = 1.0f / sqrtf(total / (float)n_w + eps);
+  const float scale = 1.0f / sqrtf(sum / (float)n_w + eps);
 #pragma unroll
   for (int i = 0; i < NORM_PER_THREAD; ++i) {
-    const int n = begin + threadIdx.x + i * NORM_THREADS;
-    if (n < end) norm_out[(size_t)t * ld_norm + n] = __float2bfloat16_rn(value[i] * scale * gain[i]);
+    const int n = threadIdx.x + i * NORM_THREADS;
+    if (n < n_w) norm_out[(size_t)t * ld_norm + n] = __float2bfloat16_rn(value[i] * scale * gain[i]);
   }
 }
 
@@ -744,16 +728,14 @@ TGE_API int tge_gemm_tcgen05_add_norm(const void* x, long long ldx, const void* 
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+norm: bad sizes M=%d N=%d K=%d", M, N, K);
   TGE_REQUIRE(status != nullptr && norm_weight != nullptr && norm_out != nullptr && eps > 0.0f, "gemm+norm: bad arguments");
   if (M == 0) return 0;
-  if (M > FUSED_MAX_TOKENS || N > NORM_CLUSTER * NORM_THREADS * NORM_PER_THREAD || scratch == nullptr) return TGE_UNSUPPORTED;
+  if (M > FUSED_MAX_TOKENS || N > NORM_THREADS * NORM_PER_THREAD || scratch == nullptr) return TGE_UNSUPPORTED;
   int splits = 0;
   int rc = launch_product(x, ldx, w, ldw, nullptr, stream_out, ldo, M, N, K, GEMM_ADD_F32, scratch, scratch_floats, 0, 0,
                           true, status, stream, &splits);
   if (rc != 1) return rc;
-  int slice = (N + NORM_CLUSTER - 1) / NORM_CLUSTER;
-  slice = (slice + 3) / 4 * 4;
-  tge_launch(splitk_add_norm_kernel, dim3(NORM_CLUSTER, M), NORM_THREADS, 0, stream,
+  tge_launch(splitk_add_norm_kernel, dim3(M), NORM_THREADS, 0, stream,
              (const float*)scratch, bias, stream_out, ldo, norm_weight, eps, (__nv_bfloat16*)norm_out, ld_norm, M, N,
-             splits, slice);
+             splits);
   return tge_launched("splitk_add_norm", 2);
 }
 
