@@ -1160,22 +1160,53 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
   const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
   const int s_lo = first_key / split_tokens;
   const int s_hi = min(pos / split_tokens, num_splits - 1);
-  float m = -INFINITY;
-  for (int s = s_lo; s <= s_hi; ++s) {
-    const size_t slot = ((size_t)s * total_tokens + t) * heads + h;
-    m = fmaxf(m, partial_ml[slot * 2]);
+  const size_t stride = (size_t)total_tokens * heads;               // slots per split
+  const size_t slot0 = (size_t)t * heads + h;
+  constexpr int HELD = 16;                                          // splits whose state is held in registers
+  if (s_hi - s_lo < HELD) {
+    // every load is asked for before the first result is needed: one round trip instead of three
+    float2 ml[HELD];
+#pragma unroll
+    for (int i = 0; i < HELD; ++i) {
+      const int s = s_lo + i;
+      ml[i] = s <= s_hi ? *reinterpret_cast<const float2*>(partial_ml + ((size_t)s * stride + slot0) * 2)
+                        : make_float2(-INFINITY, 0.0f);
+    }
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+      float o[HELD];
+#pragma unroll
+      for (int i = 0; i < HELD; ++i) {
+        const int s = s_lo + i;
+        o[i] = s <= s_hi ? partial_o[((size_t)s * stride + slot0) * HD + d] : 0.0f;
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < HELD; ++i) m = fmaxf(m, ml[i].x);
+      const float m_use = m == -INFINITY ? 0.0f : m;
+      float l = 0.0f, acc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < HELD; ++i) {          // in split order; a split beyond s_hi has m = -inf: weight 0
+        const float scale = exp2f(ml[i].x - m_use);
+        l += scale * ml[i].y;
+        acc += scale * o[i];
+      }
+      out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc * (l > 0.0f ? 1.0f / l : 0.0f));
+    }
+    return;
   }
+  float m = -INFINITY;
+  for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, partial_ml[((size_t)s * stride + slot0) * 2]);
   const float m_use = m == -INFINITY ? 0.0f : m;
   float l = 0.0f;
   for (int s = s_lo; s <= s_hi; ++s) {
-    const size_t slot = ((size_t)s * total_tokens + t) * heads + h;
+    const size_t slot = (size_t)s * stride + slot0;
     l += exp2f(partial_ml[slot * 2] - m_use) * partial_ml[slot * 2 + 1];
   }
   const float inv = l > 0.0f ? 1.0f / l : 0.0f;
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.0f;
     for (int s = s_lo; s <= s_hi; ++s) {
-      const size_t slot = ((size_t)s * total_tokens + t) * heads + h;
+      const size_t slot = (size_t)s * stride + slot0;
       acc += exp2f(partial_ml[slot * 2] - m_use) * partial_o[slot * HD + d];
     }
     out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc * inv);
