@@ -210,7 +210,8 @@ def test_generation_does_not_depend_on_pages_or_budget(model_dirs):
     prompts = [_tokens(name, n, salt=70 + n) for n in (5, 19, 64, 130)]
     params = [SamplingParams(temperature=0.8, seed=11 + i) for i in range(4)]
     outputs = []
-    for kw in (dict(max_tokens=2048, max_batch_tokens=512), dict(max_tokens=2048, max_batch_tokens=16, chunk=16),
+    for kw in (dict(max_tokens=2048, max_batch_tokens=512, run_ahead=False),
+               dict(max_tokens=2048, max_batch_tokens=512), dict(max_tokens=2048, max_batch_tokens=16, chunk=16),
                dict(num_pages=15, page_size=16, max_batch_tokens=16, chunk=16),
                dict(num_pages=13, page_size=16, max_batch_tokens=40, chunk=7),
                dict(num_pages=5, page_size=64, max_batch_tokens=40, chunk=24),
