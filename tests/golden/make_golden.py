@@ -15,6 +15,10 @@ What it does, on the CPU, touching nothing outside a temporary folder:
    steps after it, an all-rows batch, and a mixed batch of two sequences;
 5. stores tokens, the script, the logits and a hash of the weights in tests/golden/tiny_<name>.npz.
 
+6. runs the reference's sampler (src/models/sampling.cpp: sample_token; tests/golden/reference_sampler_driver.cpp)
+   on seeded logits rows with every option it has, a few hundred draws, and stores the picks in
+   tests/golden/sampler.npz.
+
 tests/test_plain_vs_golden.py then checks the plain implementation against these files.
 
     python tests/golden/make_golden.py --reference PATH_TO_THE_REFERENCE_CHECKOUT
@@ -177,7 +181,44 @@ def main():
                             row_position=np.array([r[1] for r in rows]), seed=np.array(seed),
                             weights_sha256=np.array(weights_hash(weights)), script=np.array("\n".join(lines)))
         print(f"tiny_{name}: {logits.shape[0]} rows written; weights {weights_hash(weights)[:16]}")
+    make_sampler_golden(work, tree, build)
     shutil.rmtree(work)
+
+
+def make_sampler_golden(work, tree, build):
+    driver = os.path.join(work, "reference_sampler_driver")
+    subprocess.run(["g++", "-std=c++20", "-O2", "-I", os.path.join(tree, "include"),
+                    os.path.join(HERE, "reference_sampler_driver.cpp"), os.path.join(build, "lib", "libtge_core.a"),
+                    "-lpthread", "-o", driver], check=True)
+    vocab = 331
+    rng = np.random.default_rng(77)
+    logits = (rng.standard_normal((6, vocab)) * np.array([0.5, 1.0, 2.0, 4.0, 1.0, 3.0])[:, None]).astype("<f4")
+    logits[4, [7, 90, 200]] = logits[4].max() + 1.0                 # a three-way tie at the top
+    logits_path = os.path.join(work, "sampler_logits.f32")
+    logits.tofile(logits_path)
+    history = [int(t) for t in rng.integers(0, vocab, 40)] + [7, 7, 90]
+    # row, draws, seed, temperature, top_k, top_p, min_p, repeat_penalty, penalty_window, history
+    cases = [(0, 1, 0, 0.0, 0, 1.0, 0.0, 1.0, 64, []),              # greedy
+             (4, 1, 0, 0.0, 0, 1.0, 0.0, 1.0, 64, []),              # greedy on a tie: the first index
+             (4, 1, 0, 0.0, 0, 1.0, 0.0, 1.3, 0, history),          # greedy after the penalty moved the tie
+             (1, 40, 0, 1.0, 0, 1.0, 0.0, 1.0, 64, []),             # temperature, the default seed
+             (2, 40, 12345, 0.7, 0, 1.0, 0.0, 1.0, 64, []),
+             (3, 40, 99, 1.5, 0, 1.0, 0.0, 1.0, 64, []),
+             (1, 40, 5, 1.0, 5, 1.0, 0.0, 1.0, 64, []),             # top-k
+             (2, 40, 6, 0.9, 0, 0.8, 0.0, 1.0, 64, []),             # top-p
+             (3, 40, 7, 1.2, 0, 1.0, 0.05, 1.0, 64, []),            # min-p
+             (5, 40, 8, 1.0, 50, 0.9, 0.02, 1.0, 64, []),           # all three cuts
+             (1, 40, 9, 1.0, 0, 1.0, 0.0, 1.5, 16, history),        # penalty over a window
+             (5, 40, 10, 0.8, 20, 0.95, 0.0, 1.2, 0, history)]      # cuts and penalty over the whole history
+    lines = [" ".join(str(x) for x in case[:9]) + f" {len(case[9])} " + " ".join(map(str, case[9])) for case in cases]
+    cases_path = os.path.join(work, "sampler_cases.txt")
+    open(cases_path, "w").write("\n".join(lines) + "\n")
+    out = subprocess.run([driver, logits_path, str(vocab), cases_path], check=True, capture_output=True, text=True).stdout
+    picks = [[int(t) for t in line.split()] for line in out.strip().splitlines()]
+    assert [len(p) for p in picks] == [case[1] for case in cases]
+    np.savez_compressed(os.path.join(HERE, "sampler.npz"), logits=logits, cases=np.array(lines),
+                        picks=np.array([p + [-1] * (40 - len(p)) for p in picks]))
+    print(f"sampler: {sum(len(p) for p in picks)} draws written")
 
 
 if __name__ == "__main__":
