@@ -96,6 +96,8 @@ __device__ __forceinline__ float warp_max(float v) {
 
 // Sum over a block in a fixed order: a butterfly inside each warp, then the
 // warp totals added in warp order by every thread.  `scratch` holds 32 floats.
+// Sum over the block (up to 32 warps; scratch holds 32 floats).  Every thread gets the same value: the warps'
+// sums are combined by one butterfly in every warp, in an order that depends on nothing but the block size.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int warps = (blockDim.x + 31) >> 5;
@@ -103,7 +105,5 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   __syncthreads();
   if (lane == 0) scratch[warp] = v;
   __syncthreads();
-  float total = 0.0f;
-  for (int w = 0; w < warps; ++w) total += scratch[w];
-  return total;
+  return warp_sum(lane < warps ? scratch[lane] : 0.0f);
 }
