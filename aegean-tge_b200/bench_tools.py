@@ -115,3 +115,52 @@ def bench_decode(engine, batch: int, prompt_len: int, steps: int = 64, warmup: i
     return {"batch": batch, "ms_per_step": ms, "tok_s": batch / (ms * 1e-3), "step_bytes": step_bytes, "gbs": gbs,
             "peak_gbs": peak["hbm_gbs"], "frac": gbs / peak["hbm_gbs"], "peak_source": source,
             "launches": ops.launches - launches_before, "steps": steps}
+
+
+def step_timeline(engine, batch: int, prompt_len: int, prefill: bool) -> List[Dict[str, float]]:
+    """Where one step's time goes, by kernel name, from the CUDA activity records of one step after
+    warm-up: a prompt of ``prompt_len`` tokens (``prefill``) or one token for each of ``batch`` requests
+    that hold ``prompt_len`` tokens.
+
+    A kernel launched as the dependent of another starts early and waits, so its own duration says
+    little.  What is charged to a kernel here is the time from the end of the kernel that ended before it
+    (or from its own start, if later) to its own end: the charges add up to the span of the step less the
+    gaps in which nothing ran.
+    """
+    from torch.profiler import ProfilerActivity, profile
+    vocab = engine.spec.vocab_size
+    if prefill:
+        tokens = _random_tokens(vocab, prompt_len, seed=77)
+
+        def run():
+            engine.runner.step([Portion("timeline", tokens, [prompt_len - 1])])
+            engine.runner.finish("timeline")
+        names = []
+    else:
+        names = fill_cache(engine, batch, prompt_len, prefix="timeline")
+
+        def run():
+            engine.runner.step([Portion(n, [5], [0]) for n in names])
+    for _ in range(4):
+        run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    for n in names:
+        engine.runner.finish(n)
+    events = [(e.time_range.start, e.time_range.start + e.device_time_total, e.name) for e in prof.events()
+              if e.device_time_total > 0]
+    events.sort(key=lambda e: e[1])
+    first = min(e[0] for e in events)
+    by_name: Dict[str, List[float]] = {}
+    previous_end = first
+    for start, end, raw in events:
+        name = raw.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].strip()
+        by_name.setdefault(name, []).append(end - max(previous_end, start))
+        previous_end = max(previous_end, end)
+    span = previous_end - first
+    rows = [{"kernel": name, "launches": len(v), "us": sum(v), "share": sum(v) / span} for name, v in by_name.items()]
+    rows.sort(key=lambda r: -r["us"])
+    rows.append({"kernel": "span of the step under the profiler", "launches": len(events), "us": span, "share": 1.0})
+    return rows

@@ -93,6 +93,7 @@ def build_parser() -> argparse.ArgumentParser:
     bench.add_argument("--batch", type=int, default=1)
     bench.add_argument("--n", type=int, default=64, help="decode steps to time")
     bench.add_argument("--repeat", type=int, default=3)
+    bench.add_argument("--timeline", action="store_true", help="prefill/decode: also list one step's kernels with their device times")
     # bench continuous, with the reference's names (apps/cli/main.cpp:2825-2890)
     bench.add_argument("--requests", type=int, default=8, help="continuous: requests to serve (default 8)")
     bench.add_argument("--tokens", type=int, default=32, help="continuous: tokens generated per request (default 32)")
@@ -395,6 +396,11 @@ def command_bench(args) -> int:
         print(f"decode   : batch {args.batch} at context {args.prompt_len}: {result['ms_per_step']:.3f} ms/step "
               f"({result['tok_s']:.1f} tok/s), {result['gbs']:.0f} GB/s = {result['frac']:.3f} of "
               f"{result['peak_gbs']:.0f} ({result['peak_source']})")
+    if args.timeline:
+        from .bench_tools import step_timeline
+        print("one step's time by kernel (each charged from the end of the kernel before it to its own end):")
+        for row in step_timeline(engine, args.batch, args.prompt_len, args.what == "prefill"):
+            print(f"  {row['us']:9.1f} us  {100 * row['share']:5.1f} %  x{row['launches']:<4d} {row['kernel']}")
     return 0
 
 
