@@ -468,9 +468,11 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   else {
     // Fewer, fuller waves win.  For every count of token tiles whose width (a multiple of 16) lies in
     // 128..256 the time is waves x (columns per tile + a fixed cost per tile, in columns); ties go to
-    // the wider tile.  3584 weight rows x 2048 tokens: 8 tiles of 256 are 224 items, two waves of 272;
-    // 10 tiles of 208 are 280 items, two waves of 224.
-    const int per_tile = 16;
+    // the wider tile.  The fixed cost is large: a product of 128 x N x 16 takes the tensor core about as
+    // long at N = 160 as at N = 256 (measured: a tile over K = 5,120 takes 29.4, 30.6 and 31.5 us at 160,
+    // 208 and 256 columns), so a narrower tile pays only when it saves a whole wave.  3584 weight rows x
+    // 2048 tokens: 8 tiles of 256 are 224 items, two waves; 10 tiles of 208 are 280 items, two shorter waves.
+    const int per_tile = 800;
     long long best = -1;
     bn = 256;
     for (int count = (M + 255) / 256;; ++count) {
