@@ -1,15 +1,15 @@
 // bfloat16 matrix product on the 5th-generation tensor cores: out = x . w^T (+ epilogue).
 //
-// Shape of the kernel (one persistent block per SM, 192 threads):
+// Shape of the kernel (one persistent block per SM, 320 threads):
 //   warp 0     one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle)
 //              of a 128-row weight tile and a BN-row activation tile per k-block
 //              of 64 into a ring of shared-memory stages;
 //   warp 1     allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN,
 //              K=16, float32 accumulators in tensor memory) and commits each
 //              stage back to the loader and each finished tile to the epilogue;
-//   warps 2-5  read the accumulator with tcgen05.ld (one 32-lane quarter each) and
-//              apply the epilogue, while the MMA warp already fills the second
-//              accumulator buffer with the next tile.
+//   warps 2-9  read the accumulator with tcgen05.ld (two warps per 32-lane quarter,
+//              half the columns each) and apply the epilogue, while the MMA warp
+//              already fills the second accumulator buffer with the next tile.
 // The weight rows are the M side of the instruction ("swap-AB"): a decode step
 // with 1..64 tokens still fills all 128 lanes with useful rows and streams each
 // weight byte exactly once; the token tile BN is 16..256.  Narrow outputs with
