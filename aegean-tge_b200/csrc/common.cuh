@@ -68,6 +68,27 @@ inline cudaError_t tge_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
 }
 
+// The same for a kernel whose blocks run as clusters of `cluster` along x (the grid a multiple of it).
+template <typename... KernelArgs, typename... Args>
+inline cudaError_t tge_launch_clusters(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, int cluster,
+                                       cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = cluster;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = tge_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_float(T v);
 template <>

@@ -147,6 +147,59 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// The epilogue of one finished tile: this warp's 32 lanes (weight rows n) by its columns [c_begin, c_end)
+// of the accumulator buffer `acc`.
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int acc, int quarter, int lane,
+                                              int c_begin, int c_end, int n, int tile_t, int split) {
+  const bool n_ok = n < p.n_w;
+  const float bias = (p.bias && n_ok && !p.to_partial) ? p.bias[n] : 0.0f;
+  for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+    uint32_t r[16];
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.bn + c0);
+    tc_load16(taddr, r);
+    const int m0 = tile_t * p.bn + c0;
+    if (m0 >= p.m_tok) continue;                              // uniform over the warp
+    if (!p.to_partial && p.epilogue == GEMM_ADD_F32) {
+      // read all sixteen old values before the first store, so the loads overlap
+      float* dst = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.ldo + n;
+      float old[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) old[j] = (n_ok && m0 + j < p.m_tok) ? dst[(size_t)j * p.ldo] : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + __uint_as_float(r[j]) + bias;
+      continue;
+    }
+    if (!p.to_partial && p.epilogue == GEMM_SWIGLU) {
+      // Even lanes hold gate rows, odd lanes the matching up rows.  Per pair of token columns one
+      // exchange gives the even lane (gate, up) of the first column and the odd lane those of the second.
+      const bool odd = lane & 1;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        const float a = __uint_as_float(r[j]) + bias, b = __uint_as_float(r[j + 1]) + bias;
+        const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+        const float g = odd ? got : a, u = odd ? b : got;
+        const int m = m0 + j + (odd ? 1 : 0);
+        if (n_ok && m < p.m_tok)
+          reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
+              __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
+      }
+      continue;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int m = m0 + j;
+      float v = __uint_as_float(r[j]) + bias;
+      if (p.to_partial) {
+        if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
+      } else if (n_ok && m < p.m_tok) {
+        if (p.epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+      }
+    }
+  }
+}
+
 // ---- the kernel ------------------------------------------------------------
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -304,54 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int tile_t = rest % p.tiles_t, tile_w = rest / p.tiles_t;
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int n = tile_w * BM + quarter * 32 + lane;          // weight row = output feature
-      const bool n_ok = n < p.n_w;
-      const float bias = (p.bias && n_ok && !p.to_partial) ? p.bias[n] : 0.0f;
-      for (int c0 = c_begin; c0 < c_end; c0 += 16) {
-        uint32_t r[16];
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * p.bn + c0);
-        tc_load16(taddr, r);
-        const int m0 = tile_t * p.bn + c0;
-        if (m0 >= p.m_tok) continue;                              // uniform over the warp
-        if (!p.to_partial && p.epilogue == GEMM_ADD_F32) {
-          // read all sixteen old values before the first store, so the loads overlap
-          float* dst = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.ldo + n;
-          float old[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) old[j] = (n_ok && m0 + j < p.m_tok) ? dst[(size_t)j * p.ldo] : 0.0f;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + __uint_as_float(r[j]) + bias;
-          continue;
-        }
-        if (!p.to_partial && p.epilogue == GEMM_SWIGLU) {
-          // Even lanes hold gate rows, odd lanes the matching up rows.  Per pair of token columns one
-          // exchange gives the even lane (gate, up) of the first column and the odd lane those of the second.
-          const bool odd = lane & 1;
-#pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            const float a = __uint_as_float(r[j]) + bias, b = __uint_as_float(r[j + 1]) + bias;
-            const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
-            const float g = odd ? got : a, u = odd ? b : got;
-            const int m = m0 + j + (odd ? 1 : 0);
-            if (n_ok && m < p.m_tok)
-              reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
-                  __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
-          }
-          continue;
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m0 + j;
-          float v = __uint_as_float(r[j]) + bias;
-          if (p.to_partial) {
-            if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
-          } else if (n_ok && m < p.m_tok) {
-            if (p.epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-          }
-        }
-      }
+      epilogue_tile(p, tmem_base, acc, quarter, lane, c_begin, c_end, tile_w * BM + quarter * 32 + lane, tile_t, split);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -364,6 +370,196 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)p.acc_cols) : "memory");
+  }
+}
+
+// ---- two SMs on one tile ------------------------------------------------------
+// A pair of blocks (a cluster of two) owns a tile of 256 weight rows by BN tokens.  Each block copies its
+// own 128 weight rows and its own half of the token rows into its own shared memory; one thread of the
+// even block issues tcgen05.mma.cta_group::2 (M = 256), which reads the weight rows of each block for that
+// block's accumulator lanes and the token rows of both for all of them, so every SM fetches half as many
+// token rows per product as when it works alone.  Each block's tensor memory ends up holding its 128 rows
+// by BN columns, in the layout of the one-SM kernel, and each block runs the same epilogue on it.
+// Barriers: the copies of both blocks complete on the even block's full barrier; a commit of the issuing
+// thread arrives on the empty (and accumulator-full) barrier at the same offset in both blocks; the epilogue
+// warps of both blocks arrive on the even block's accumulator-empty barrier.  Waits are bounded as above;
+// both blocks meet at a cluster barrier before tensor memory is freed, so neither leaves while the other may
+// still signal it.
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+// the address, in the cluster's shared window, of `addr` of this block as seen in block `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.aligned;\nbarrier.cluster.wait.aligned;\n" ::: "memory");
+}
+// copy into this block's shared memory, bytes counted on a barrier that may live in the other block of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// arrives on the barrier at this offset in both blocks of the pair once the products issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  const uint32_t zero = 0;      // no output lane is switched off
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}\n"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+
+constexpr int PAIR_BM = 2 * BM;          // weight rows per tile of a pair
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                         const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t b_half_bytes = (uint32_t)(p.bn / 2) * BK * 2;          // this block's half of the token rows
+  const uint32_t stage_bytes = A_STAGE_BYTES + b_half_bytes;
+  const uint32_t bars = base + (uint32_t)p.stages * stage_bytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (p.stages + s); };
+  auto tfull_bar = [&](int s) { return bars + 8u * (2 * p.stages + s); };
+  auto tempty_bar = [&](int s) { return bars + 8u * (2 * p.stages + 2 + s); };
+  const uint32_t tmem_slot = bars + 8u * (2 * p.stages + 4);
+  unsigned char* generic_base = smem_raw + (base - raw);
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(generic_base + (size_t)p.stages * stage_bytes + 8u * (2 * p.stages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot_ptr + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();                                 // 0: issues the products; 1: its partner
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);                                        // used in the even block only
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 2 * EPI_WARPS);                          // used in the even block only
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    // one warp of each block, the same warp in both, the same place for the address in both
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tmem_slot), "r"((uint32_t)p.acc_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  __syncwarp();
+  tc_fence_before();
+  cluster_sync_all();             // both blocks' barriers exist before either signals the other
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_trigger();
+  pdl_wait();
+
+  const int total_work = p.tiles_w * p.tiles_t;
+  const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------ TMA loader (both blocks) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int work = pair; work < total_work && ok; work += pairs) {
+        const int tile_t = work % p.tiles_t, tile_w = work / p.tiles_t;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * stage_bytes);
+          const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
+          const uint32_t a_dst = base + (uint32_t)stage * stage_bytes;
+          tma_load_2d_pair(a_dst, &map_w, leader_full, kb * BK, tile_w * PAIR_BM + (int)rank * BM);
+          tma_load_2d_pair(a_dst + A_STAGE_BYTES, &map_x, leader_full, kb * BK, tile_t * p.bn + (int)rank * (p.bn / 2));
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // copies may still be on their way into this block's shared memory: give them time
+        const unsigned long long start = global_timer();
+        while (global_timer() - start < 1000000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even block) ------------------------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(PAIR_BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int work = pair; work < total_work && ok; work += pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.bn);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = base + (uint32_t)stage * stage_bytes;
+          const uint32_t b_addr = a_addr + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t desc_a = make_smem_desc(a_addr + k * UMMA_K * 2);
+            const uint64_t desc_b = make_smem_desc(b_addr + k * UMMA_K * 2);
+            tc_mma_pair(d_tmem, desc_a, desc_b, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(stage));
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both blocks) -------------------------------
+    const int quarter = warp & 3;
+    const int column_half = (warp - 2) >> 2;
+    const int first_half = ((p.bn / 16 + 1) / 2) * 16;
+    const int c_begin = column_half == 0 ? 0 : first_half;
+    const int c_end = column_half == 0 ? first_half : p.bn;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int work = pair; work < total_work && ok; work += pairs) {
+      const int tile_t = work % p.tiles_t, tile_w = work / p.tiles_t;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      epilogue_tile(p, tmem_base, acc, quarter, lane, c_begin, c_end,
+                    tile_w * PAIR_BM + (int)rank * BM + quarter * 32 + lane, tile_t, 0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_rank(tempty_bar(acc), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  cluster_sync_all();             // nobody of the pair is still computing, copying or signalling
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)p.acc_cols) : "memory");
   }
 }
 
@@ -514,7 +710,76 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   return plan;
 }
 
+// ---- pairs of SMs ----
+int g_pair_mode = 1;      // 0: never; 1: where it is expected to be faster; 2: wherever the kernel can run
+
+// How many pairs of blocks of the pair kernel the GPU holds at once; 0 when it cannot be launched.
+int pair_capacity() {
+  static int capacity = -1;
+  if (capacity >= 0) return capacity;
+  capacity = 0;
+  if (getenv("TGE_NO_PAIR_GEMM") != nullptr) return capacity;
+  if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess) {
+    cudaGetLastError();
+    return capacity;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(sm_count() / 2 * 2);
+  config.blockDim = dim3(NUM_THREADS);
+  config.dynamicSmemBytes = SMEM_LIMIT;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 2;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel, &config) == cudaSuccess && clusters > 0)
+    capacity = clusters < sm_count() / 2 ? clusters : sm_count() / 2;
+  else
+    cudaGetLastError();
+  return capacity;
+}
+
+// The token tile of the pair kernel and what the product then costs, in the units of make_plan's chooser.
+Plan make_pair_plan(int M, int N, int K, int pairs, long long* cost_out) {
+  Plan plan;
+  const int tiles_w = (N + PAIR_BM - 1) / PAIR_BM;
+  const int per_tile = 800;
+  int bn;
+  long long best = -1;
+  if (M <= 128) {
+    bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    best = (long long)(tiles_w + pairs - 1) / pairs * (bn + per_tile);
+  } else {
+    bn = 256;
+    for (int count = (M + 255) / 256;; ++count) {
+      const int width = ((M + count - 1) / count + 15) / 16 * 16;
+      if (width < 128) break;
+      const long long items = (long long)tiles_w * ((M + width - 1) / width);
+      const long long cost = (items + pairs - 1) / pairs * (width + per_tile);
+      if (best < 0 || cost < best) { best = cost; bn = width; }
+    }
+  }
+  plan.bn = bn;
+  const int stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
+  int stages = (SMEM_LIMIT - 2048) / stage_bytes;
+  if (stages > MAX_STAGES) stages = MAX_STAGES;
+  const int k_blocks = (K + BK - 1) / BK;
+  if (stages > k_blocks) stages = k_blocks < 2 ? 2 : k_blocks;
+  plan.stages = stages;
+  plan.splits = 1;
+  *cost_out = best;
+  return plan;
+}
+
 }  // namespace
+
+// 0: never pair two SMs on a tile; 1: where it is expected to be faster (the default); 2: wherever possible.
+TGE_API void tge_gemm_tcgen05_pair_mode(int mode) { g_pair_mode = mode; }
+// How many pairs of SMs the pair kernel occupies at once (0: it cannot run here or is switched off).
+TGE_API int tge_gemm_tcgen05_pair_capacity() { return pair_capacity(); }
 
 // How many float32 of scratch the product would like (0 when it will not split along k).
 TGE_API long long tge_gemm_tcgen05_scratch_floats(int M, int N, int K) {
@@ -542,6 +807,45 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   CUtensorMap map_w, map_x;
   int rc = make_map(&map_w, w, N, K, ldw, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (rc != 0) return rc;
+
+  if (g_pair_mode > 0 && !partial_always && (!to_partial || g_pair_mode == 2) && force_bn == 0 && force_splits == 0 &&
+      (M > 128 || g_pair_mode == 2)) {
+    const int pairs = pair_capacity();
+    if (pairs > 0) {
+      long long pair_cost = 0;
+      const Plan pair_plan = make_pair_plan(M, N, K, pairs, &pair_cost);
+      const long long single_items = (long long)((N + BM - 1) / BM) * ((M + plan.bn - 1) / plan.bn);
+      const long long single_cost = (single_items + sm_count() - 1) / sm_count() * (plan.bn + 800);
+      static const int min_waves = getenv("TGE_PAIR_MIN_WAVES") ? atoi(getenv("TGE_PAIR_MIN_WAVES")) : 4;
+      const long long pair_items = (long long)((N + PAIR_BM - 1) / PAIR_BM) * ((M + pair_plan.bn - 1) / pair_plan.bn);
+      if (g_pair_mode == 2 || (pair_cost <= single_cost && pair_items >= (long long)min_waves * pairs)) {
+        rc = make_map(&map_x, x, M, K, ldx, pair_plan.bn / 2, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (rc != 0) return rc;
+        GemmParams p;
+        p.n_w = N; p.m_tok = M; p.K = K;
+        p.bn = pair_plan.bn; p.stages = pair_plan.stages; p.splits = 1;
+        p.k_blocks = (K + BK - 1) / BK;
+        p.tiles_w = (N + PAIR_BM - 1) / PAIR_BM;
+        p.tiles_t = (M + pair_plan.bn - 1) / pair_plan.bn;
+        p.epilogue = epilogue;
+        int cols = 32;
+        while (cols < 2 * pair_plan.bn) cols *= 2;
+        p.acc_cols = cols;
+        p.to_partial = 0;
+        p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
+        const size_t smem = 1024 + (size_t)pair_plan.stages * (A_STAGE_BYTES + (pair_plan.bn / 2) * BK * 2) +
+                            8 * (2 * pair_plan.stages + 4) + 16;
+        const long long total = (long long)p.tiles_w * p.tiles_t;
+        const int grid = 2 * (int)(total < pairs ? total : pairs);
+        tge_launch_clusters(gemm_tcgen05_pair_kernel, grid, NUM_THREADS, smem, 2, stream, map_w, map_x, p);
+        rc = tge_check_launch("gemm_tcgen05_pair");
+        if (rc != 0) return rc;
+        *splits_out = 0;
+        return 1;
+      }
+    }
+  }
+
   rc = make_map(&map_x, x, M, K, ldx, plan.bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (rc != 0) return rc;
 

@@ -74,6 +74,8 @@ def core() -> ctypes.CDLL:
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                     _c_ptr, _c_ll, _c_ptr, _c_ptr])
+        lib.tge_gemm_tcgen05_pair_mode.argtypes = [_c_int]
+        lib.tge_gemm_tcgen05_pair_mode.restype = None
         lib.tge_gemm_tcgen05_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_gemm_tcgen05_scratch_floats.restype = _c_ll
         _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
@@ -336,6 +338,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
     _check(lib.tge_gemm_simt(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                              int(x.dtype == torch.bfloat16), epilogue, _stream()), lib)
     return out
+
+
+def set_pair_gemm(mode: int) -> None:
+    """Whether the bfloat16 product may pair two SMs on one tile: 0 never, 1 where it is expected to be
+    faster (the default), 2 wherever the kernel can run (tests)."""
+    core().tge_gemm_tcgen05_pair_mode(int(mode))
 
 
 FUSED_MAX_TOKENS = 256      # small batches: product + one kernel per token row; larger ones use separate kernels

@@ -165,6 +165,47 @@ def test_gemm_tcgen05_epilogues(ops, M, N, K, splits):
     ops.check_status()
 
 
+@pytest.fixture
+def pair_everywhere(ops):
+    """Every bfloat16 product that the two-SM kernel can run goes to it, also shapes it would not be chosen for."""
+    ops.set_pair_gemm(2)
+    yield
+    ops.set_pair_gemm(1)
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES + [(2048, 768, 192), (257, 130, 136), (140, 3584, 64), (1000, 520, 1032)])
+def test_gemm_pair_exact_on_small_integers(ops, pair_everywhere, M, N, K):
+    """The kernel that pairs two SMs on a tile of 256 weight rows: rows of either block, token halves of
+    either block, ragged edges in both directions, more k-blocks than stages."""
+    gen = torch.Generator().manual_seed(M + N + K)
+    x = torch.randint(-2, 3, (M, K), generator=gen).to(torch.bfloat16)
+    w = torch.randint(-3, 4, (N, K), generator=gen).to(torch.bfloat16)
+    ref = (x.double() @ w.double().T).float()
+    out = ops.linear(x.to(DEV), w.to(DEV), None, ops.GEMM_STORE_F32)
+    ops.check_status()
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("M,N,K", [(9, 260, 328), (150, 384, 704), (2048, 512, 256), (1100, 640, 192)])
+def test_gemm_pair_epilogues(ops, pair_everywhere, M, N, K):
+    gen = torch.Generator().manual_seed(7 * M)
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=gen) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=gen)
+    ref = ops_plain.linear(x, w, b)
+    out = ops.linear(x.to(DEV), w.to(DEV), b.to(DEV), ops.GEMM_STORE)
+    assert out.dtype == torch.bfloat16 and rel_error(out, ref) < TOL[torch.bfloat16]
+    out = ops.linear(x.to(DEV), w.to(DEV), b.to(DEV), ops.GEMM_STORE_F32)
+    assert rel_error(out, ref) < 2e-5
+    stream = torch.randn(M, N, generator=gen)
+    d = stream.to(DEV)
+    ops.linear(x.to(DEV), w.to(DEV), None, ops.GEMM_ADD_F32, out=d)
+    assert rel_error(d, stream.double() + ops_plain.linear(x, w, None)) < 2e-5
+    out = ops.linear(x.to(DEV), w.to(DEV), None, ops.GEMM_SWIGLU)
+    assert out.shape == (M, N // 2) and rel_error(out, ops_plain.swiglu_interleaved(x, w)) < TOL[torch.bfloat16]
+    ops.check_status()
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address(ops):
     """K that is no multiple of 8 cannot be a TMA row pitch: the product still comes out right (CUDA cores)."""
     gen = torch.Generator().manual_seed(11)
