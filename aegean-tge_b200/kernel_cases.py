@@ -23,6 +23,7 @@ EPILOGUES = {"store": ops.GEMM_STORE, "f32": ops.GEMM_STORE_F32, "add": ops.GEMM
 def run_gemm(args) -> None:
     dev = "cuda:0"
     epilogue = EPILOGUES[args.epilogue]
+    ops.set_pair_gemm(args.pair)
     copies = max(2, int(300e6 // (args.n * args.k * 2)) + 1)
     weights = [torch.randn(args.n, args.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     x = torch.randn(args.m, args.k, device=dev, dtype=torch.bfloat16)
@@ -84,6 +85,8 @@ def main(argv=None) -> int:
     gemm.add_argument("--k", type=int, default=3584)
     gemm.add_argument("--epilogue", choices=sorted(EPILOGUES), default="swiglu")
     gemm.add_argument("--repeat", type=int, default=8)
+    gemm.add_argument("--pair", type=int, default=1, choices=[0, 1, 2],
+                      help="two SMs on one tile: 0 never, 1 where the product has many waves (default), 2 always")
     attn = sub.add_parser("attention")
     attn.add_argument("--batch", type=int, default=8)
     attn.add_argument("--context", type=int, default=2048)
