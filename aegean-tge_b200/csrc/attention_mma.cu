@@ -665,7 +665,7 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   if (warp == DEC_WARPS) {
     // The loading warp runs ahead of the others by up to a ring of tiles; nobody waits for anybody else
     // block-wide.  A stage is refilled once all computing warps have released it.
-    if (lane == 0) {
+    if (elect_one()) {
       for (int tile = 0; tile < num_tiles; ++tile) {
         if (tile >= DEC_STAGES)
           mbar_wait_bounded(empty_bar(tile % DEC_STAGES), (uint32_t)(tile / DEC_STAGES - 1) & 1u, p.status);
@@ -931,7 +931,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
   };
   if (warp == PRE_WARPS) {
     // the loading warp: a stage is refilled as soon as all eight computing warps have released it
-    if (lane == 0) {
+    if (elect_one()) {
       for (int tile = 0; tile < num_tiles; ++tile) {
         if (tile >= PRE_STAGES)
           mbar_wait_bounded(bars + 8 * (PRE_STAGES + tile % PRE_STAGES), (uint32_t)(tile / PRE_STAGES - 1) & 1u, p.status);

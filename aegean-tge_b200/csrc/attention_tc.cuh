@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
     }
   } else if (warp == 4) {
     // ------------------------------- products -------------------------------
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       const uint64_t q_desc = desc_k_major(q_smem);

@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc2_kernel(
     // S = Q K^T of key tile j for both query tiles, into their score buffers (j & 1).  A buffer is free
     // once the softmax warps have read tile j - 2 out of it (a barrier of its own: a waiter that could fall
     // two phases behind cannot tell them apart by parity).
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BKV >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       for (int tile = 0; tile < num_tiles; ++tile) {
         const int stage = tile % STAGES;
@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc2_kernel(
     }
   } else if (warp == MMA_WARP) {
     // ------------------------------- P V products -------------------------------
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
       for (int it = 0; it < num_tiles; ++it) {
         const int stage = it % STAGES;

@@ -49,6 +49,16 @@ constexpr int TGE_UNSUPPORTED = -100;  // shape outside what the kernel takes; n
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
+// True in exactly one lane of a converged warp.  A role that one thread plays is entered through this and
+// not through `lane == 0`: the compiler then knows the region to be uniform and keeps the addresses and
+// descriptors of the TMA and tcgen05 instructions in uniform registers (measured: the one-SM products of a
+// 2,048-token prefill 2-9 % faster, the decode products 3-4 %, the two-SM products 4-13 %).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+  return chosen != 0;
+}
+
 bool tge_pdl_enabled();
 
 // Launches `kernel` so that it may start while its predecessor in the stream drains (see above).

@@ -256,7 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------ TMA loader ------------------------------
-    if (lane == 0) {
+    if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       int issued = 0;
@@ -308,7 +308,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
@@ -477,7 +477,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 
   if (warp == 0) {
     // ------------------------------ TMA loader (both blocks) ------------------------------
-    if (lane == 0) {
+    if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -501,7 +501,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (even block) ------------------------------
-    if (lane == 0 && rank == 0) {
+    if (rank == 0 && elect_one()) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(PAIR_BM >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
@@ -816,9 +816,7 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
       const Plan pair_plan = make_pair_plan(M, N, K, pairs, &pair_cost);
       const long long single_items = (long long)((N + BM - 1) / BM) * ((M + plan.bn - 1) / plan.bn);
       const long long single_cost = (single_items + sm_count() - 1) / sm_count() * (plan.bn + 800);
-      static const int min_waves = getenv("TGE_PAIR_MIN_WAVES") ? atoi(getenv("TGE_PAIR_MIN_WAVES")) : 4;
-      const long long pair_items = (long long)((N + PAIR_BM - 1) / PAIR_BM) * ((M + pair_plan.bn - 1) / pair_plan.bn);
-      if (g_pair_mode == 2 || (pair_cost <= single_cost && pair_items >= (long long)min_waves * pairs)) {
+      if (g_pair_mode == 2 || pair_cost <= single_cost) {
         rc = make_map(&map_x, x, M, K, ldx, pair_plan.bn / 2, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
         if (rc != 0) return rc;
         GemmParams p;

@@ -86,7 +86,7 @@ def main(argv=None) -> int:
     gemm.add_argument("--epilogue", choices=sorted(EPILOGUES), default="swiglu")
     gemm.add_argument("--repeat", type=int, default=8)
     gemm.add_argument("--pair", type=int, default=1, choices=[0, 1, 2],
-                      help="two SMs on one tile: 0 never, 1 where the product has many waves (default), 2 always")
+                      help="two SMs on one tile: 0 never, 1 where its cost model says so (default), 2 always")
     attn = sub.add_parser("attention")
     attn.add_argument("--batch", type=int, default=8)
     attn.add_argument("--context", type=int, default=2048)
