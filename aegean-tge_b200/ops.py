@@ -135,7 +135,13 @@ def _check(rc: int, lib: ctypes.CDLL) -> int:
     return rc
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current stream's handle (asked on every launch: a graph capture switches streams)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
