@@ -603,7 +603,7 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   auto empty_bar = [&](int s) { return bars + 8u * (DEC_STAGES + s); };
   int* local_table = reinterpret_cast<int*>(generic + DEC_STAGES * TMA_STAGE_BYTES + 64);
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = uniform_warp_index();
   const int g8 = lane >> 2, t4 = lane & 3;
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int token = p.q_start[seq];
@@ -848,7 +848,7 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
   const uint32_t bars = base + PRE_STAGES * TMA_STAGE_BYTES;            // full[stages], then empty[stages]
   int* local_table = reinterpret_cast<int*>(generic + PRE_STAGES * TMA_STAGE_BYTES + 128);
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = uniform_warp_index();
   const int g8 = lane >> 2, t4 = lane & 3;
   const int kvh = blockIdx.y, split = blockIdx.z;
   if (tid == 0) {

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
                  v_bar = s_bar + 32;
   int* local_table = reinterpret_cast<int*>(generic + (stages - base) + STAGES * TMA_STAGE_BYTES + 128);   // after the barriers
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = uniform_warp_index();
   // Blocks are handed out in the order of blockIdx.x: the kv head changes fastest, so that the long tiles of
   // every kv head start first and the short ones fill the gaps (with the kv head as blockIdx.y, a whole kv
   // head's long tiles started only after the first ones' short tiles).

@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc2_kernel(
   const uint32_t free_bar = o_bar + 8 * QTILES;           // [query tile][score buffer]: the softmax has read the scores
   int* local_table = reinterpret_cast<int*>(generic + (stages - base) + STAGES * TMA_STAGE_BYTES + BARRIER_BYTES);
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = uniform_warp_index();
   const int kvh = (int)blockIdx.x % p.kv_heads, pair_rank = (int)blockIdx.x / p.kv_heads, split = blockIdx.z;
   pdl_wait();
   if (tid == 0) {

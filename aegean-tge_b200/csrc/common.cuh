@@ -59,6 +59,10 @@ __device__ __forceinline__ bool elect_one() {
   return chosen != 0;
 }
 
+// The index of the calling warp in its block, in a form the compiler knows to be the same in all its lanes
+// (a broadcast from lane 0), so that branches on a warp's role and addresses derived from it stay uniform.
+__device__ __forceinline__ int uniform_warp_index() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+
 bool tge_pdl_enabled();
 
 // Launches `kernel` so that it may start while its predecessor in the stream drains (see above).

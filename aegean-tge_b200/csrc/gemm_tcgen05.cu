@@ -222,7 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       reinterpret_cast<volatile uint32_t*>(generic_base + (size_t)p.stages * stage_bytes + 8u * (2 * p.stages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot_ptr + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -443,7 +443,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
       reinterpret_cast<volatile uint32_t*>(generic_base + (size_t)p.stages * stage_bytes + 8u * (2 * p.stages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot_ptr + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = uniform_warp_index(), lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();                                 // 0: issues the products; 1: its partner
 
   if (threadIdx.x == 0) {
