@@ -472,7 +472,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
   pdl_trigger();
   pdl_wait();
 
-  const int total_work = p.tiles_w * p.tiles_t;
+  const int total_work = p.tiles_w * p.tiles_t * p.splits;
   const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
 
   if (warp == 0) {
@@ -482,8 +482,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
       uint32_t phase = 0;
       bool ok = true;
       for (int work = pair; work < total_work && ok; work += pairs) {
-        const int tile_t = work % p.tiles_t, tile_w = work / p.tiles_t;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int split = work % p.splits;
+        const int rest = work / p.splits;
+        const int tile_t = rest % p.tiles_t, tile_w = rest / p.tiles_t;
+        const int kb_begin = (int)((long long)split * p.k_blocks / p.splits);
+        const int kb_end = (int)((long long)(split + 1) * p.k_blocks / p.splits);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
           if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * stage_bytes);
           const uint32_t leader_full = map_to_rank(full_bar(stage), 0);
@@ -509,10 +513,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int work = pair; work < total_work && ok; work += pairs) {
+        const int split = work % p.splits;
+        const int kb_begin = (int)((long long)split * p.k_blocks / p.splits);
+        const int kb_end = (int)((long long)(split + 1) * p.k_blocks / p.splits);
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, p.status, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.bn);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.status, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = base + (uint32_t)stage * stage_bytes;
@@ -521,7 +528,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t desc_a = make_smem_desc(a_addr + k * UMMA_K * 2);
             const uint64_t desc_b = make_smem_desc(b_addr + k * UMMA_K * 2);
-            tc_mma_pair(d_tmem, desc_a, desc_b, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma_pair(d_tmem, desc_a, desc_b, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
           tc_commit_pair(empty_bar(stage));
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -542,11 +549,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int work = pair; work < total_work && ok; work += pairs) {
-      const int tile_t = work % p.tiles_t, tile_w = work / p.tiles_t;
+      const int split = work % p.splits;
+      const int rest = work / p.splits;
+      const int tile_t = rest % p.tiles_t, tile_w = rest / p.tiles_t;
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, abort_flag)) { ok = false; break; }
       tc_fence_after();
       epilogue_tile(p, tmem_base, acc, quarter, lane, c_begin, c_end,
-                    tile_w * PAIR_BM + (int)rank * BM + quarter * 32 + lane, tile_t, 0);
+                    tile_w * PAIR_BM + (int)rank * BM + quarter * 32 + lane, tile_t, split);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_rank(tempty_bar(acc), 0));
@@ -742,49 +751,88 @@ int pair_capacity() {
   return capacity;
 }
 
-// The token tile of the pair kernel and what the product then costs, in the units of make_plan's chooser.
-Plan make_pair_plan(int M, int N, int K, int pairs, long long* cost_out) {
+// What a plan costs, in k-blocks of a 256-column tile: waves of the grid x (k-blocks per item + a fixed
+// cost per item) x the time of a k-block at this tile width relative to 256 columns (a k-block of 128 x N x 64
+// takes the tensor core about as long at N = 160 as at N = 256, hence the large constant).
+// A cut along k adds a kernel that sums the partial sums (about 3 us) and their way to memory and back (at about
+// 4 TB/s); a k-block of a 256-column tile, 1,056 units, takes about a third of a microsecond.
+long long plan_cost(long long items, int places, int k_blocks, int splits, int bn, long long outputs) {
+  const long long waves = (items * splits + places - 1) / places;
+  long long cost = waves * ((k_blocks + splits - 1) / splits + 6) * (bn + 800);
+  if (splits > 1) cost += 3000 * 3 + (long long)((double)splits * outputs * 8.0 / 4.0e6 * 3000.0);
+  return cost;
+}
+
+// Token tile and cut along k of the pair kernel: the widest tiles first, then enough splits to fill the pairs.
+Plan make_pair_plan(int M, int N, int K, int pairs, long long scratch_floats, long long* cost_out) {
   Plan plan;
   const int tiles_w = (N + PAIR_BM - 1) / PAIR_BM;
-  const int per_tile = 800;
-  int bn;
+  const int k_blocks = (K + BK - 1) / BK;
+  int first_width;
+  if (M <= 16) first_width = 16;
+  else if (M <= 32) first_width = 32;
+  else if (M <= 64) first_width = 64;
+  else if (M <= 128) first_width = 128;
+  else first_width = 0;
   long long best = -1;
-  if (M <= 128) {
-    bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    best = (long long)(tiles_w + pairs - 1) / pairs * (bn + per_tile);
-  } else {
-    bn = 256;
-    for (int count = (M + 255) / 256;; ++count) {
-      const int width = ((M + count - 1) / count + 15) / 16 * 16;
-      if (width < 128) break;
-      const long long items = (long long)tiles_w * ((M + width - 1) / width);
-      const long long cost = (items + pairs - 1) / pairs * (width + per_tile);
-      if (best < 0 || cost < best) { best = cost; bn = width; }
+  plan.bn = 256;
+  plan.splits = 1;
+  for (int count = (M + 255) / 256;; ++count) {
+    const int width = first_width ? first_width : ((M + count - 1) / count + 15) / 16 * 16;
+    if (!first_width && width < 128) break;
+    const long long items = (long long)tiles_w * ((M + width - 1) / width);
+    const int most = items >= pairs || k_blocks < 8 ? 1 : (k_blocks / 4 < 32 ? k_blocks / 4 : 32);
+    for (int splits = 1; splits <= most; ++splits) {
+      if (splits > 1 && (long long)splits * M * N > scratch_floats) break;
+      const long long cost = plan_cost(items, pairs, k_blocks, splits, width, (long long)M * N);
+      if (best < 0 || cost < best) { best = cost; plan.bn = width; plan.splits = splits; }
     }
+    if (first_width) break;
   }
-  plan.bn = bn;
-  const int stage_bytes = A_STAGE_BYTES + (bn / 2) * BK * 2;
+  const int stage_bytes = A_STAGE_BYTES + (plan.bn / 2) * BK * 2;
   int stages = (SMEM_LIMIT - 2048) / stage_bytes;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
-  const int k_blocks = (K + BK - 1) / BK;
   if (stages > k_blocks) stages = k_blocks < 2 ? 2 : k_blocks;
   plan.stages = stages;
-  plan.splits = 1;
   *cost_out = best;
   return plan;
+}
+
+// Whether the pair kernel takes this product, and with which plan.
+bool choose_pair(int M, int N, int K, long long scratch_floats, const Plan& single, int force_bn, int force_splits,
+                 Plan* pair_plan) {
+  if (g_pair_mode <= 0 || force_bn != 0 || force_splits != 0 || (M <= 128 && g_pair_mode != 2)) return false;
+  const int pairs = pair_capacity();
+  if (pairs <= 0) return false;
+  long long pair_cost = 0;
+  *pair_plan = make_pair_plan(M, N, K, pairs, scratch_floats, &pair_cost);
+  const long long single_items = (long long)((N + BM - 1) / BM) * ((M + single.bn - 1) / single.bn);
+  const long long single_cost = plan_cost(single_items, sm_count(), (K + BK - 1) / BK, single.splits, single.bn, (long long)M * N);
+  return g_pair_mode == 2 || pair_cost <= single_cost;
 }
 
 }  // namespace
 
 // 0: never pair two SMs on a tile; 1: where it is expected to be faster (the default); 2: wherever possible.
 TGE_API void tge_gemm_tcgen05_pair_mode(int mode) { g_pair_mode = mode; }
+// What the product of these sizes would run as: out = {two SMs per tile?, token tile, stages, k-splits}.
+TGE_API void tge_gemm_tcgen05_describe(int M, int N, int K, int* out) {
+  const Plan plan = make_plan(M, N, K, (long long)1 << 60, 0, 0);
+  Plan pair_plan;
+  const bool pair = choose_pair(M, N, K, (long long)1 << 60, plan, 0, 0, &pair_plan);
+  const Plan& used = pair ? pair_plan : plan;
+  out[0] = pair ? 1 : 0; out[1] = used.bn; out[2] = used.stages; out[3] = used.splits;
+}
 // How many pairs of SMs the pair kernel occupies at once (0: it cannot run here or is switched off).
 TGE_API int tge_gemm_tcgen05_pair_capacity() { return pair_capacity(); }
 
 // How many float32 of scratch the product would like (0 when it will not split along k).
 TGE_API long long tge_gemm_tcgen05_scratch_floats(int M, int N, int K) {
-  Plan plan = make_plan(M, N, K, (long long)1 << 60, 0, 0);
-  return plan.splits > 1 ? (long long)plan.splits * M * N : 0;
+  const Plan plan = make_plan(M, N, K, (long long)1 << 60, 0, 0);
+  int splits = plan.splits;
+  Plan pair_plan;
+  if (choose_pair(M, N, K, (long long)1 << 60, plan, 0, 0, &pair_plan) && pair_plan.splits > splits) splits = pair_plan.splits;
+  return splits > 1 ? (long long)splits * M * N : 0;
 }
 
 namespace {
@@ -808,40 +856,36 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   int rc = make_map(&map_w, w, N, K, ldw, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (rc != 0) return rc;
 
-  if (g_pair_mode > 0 && !partial_always && (!to_partial || g_pair_mode == 2) && force_bn == 0 && force_splits == 0 &&
-      (M > 128 || g_pair_mode == 2)) {
+  Plan pair_plan;
+  if (choose_pair(M, N, K, scratch_floats, plan, force_bn, force_splits, &pair_plan)) {
+    const bool pair_partial = partial_always || pair_plan.splits > 1;
+    TGE_REQUIRE(!pair_partial || (long long)pair_plan.splits * M * N <= scratch_floats,
+                "gemm_tcgen05: %d k-splits need %lld floats of scratch, have %lld", pair_plan.splits,
+                (long long)pair_plan.splits * M * N, scratch_floats);
+    rc = make_map(&map_x, x, M, K, ldx, pair_plan.bn / 2, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != 0) return rc;
+    GemmParams p;
+    p.n_w = N; p.m_tok = M; p.K = K;
+    p.bn = pair_plan.bn; p.stages = pair_plan.stages; p.splits = pair_plan.splits;
+    p.k_blocks = (K + BK - 1) / BK;
+    p.tiles_w = (N + PAIR_BM - 1) / PAIR_BM;
+    p.tiles_t = (M + pair_plan.bn - 1) / pair_plan.bn;
+    p.epilogue = epilogue;
+    int cols = 32;
+    while (cols < 2 * pair_plan.bn) cols *= 2;
+    p.acc_cols = cols;
+    p.to_partial = pair_partial ? 1 : 0;
+    p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
+    const size_t smem = 1024 + (size_t)pair_plan.stages * (A_STAGE_BYTES + (pair_plan.bn / 2) * BK * 2) +
+                        8 * (2 * pair_plan.stages + 4) + 16;
+    const long long total = (long long)p.tiles_w * p.tiles_t * p.splits;
     const int pairs = pair_capacity();
-    if (pairs > 0) {
-      long long pair_cost = 0;
-      const Plan pair_plan = make_pair_plan(M, N, K, pairs, &pair_cost);
-      const long long single_items = (long long)((N + BM - 1) / BM) * ((M + plan.bn - 1) / plan.bn);
-      const long long single_cost = (single_items + sm_count() - 1) / sm_count() * (plan.bn + 800);
-      if (g_pair_mode == 2 || pair_cost <= single_cost) {
-        rc = make_map(&map_x, x, M, K, ldx, pair_plan.bn / 2, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-        if (rc != 0) return rc;
-        GemmParams p;
-        p.n_w = N; p.m_tok = M; p.K = K;
-        p.bn = pair_plan.bn; p.stages = pair_plan.stages; p.splits = 1;
-        p.k_blocks = (K + BK - 1) / BK;
-        p.tiles_w = (N + PAIR_BM - 1) / PAIR_BM;
-        p.tiles_t = (M + pair_plan.bn - 1) / pair_plan.bn;
-        p.epilogue = epilogue;
-        int cols = 32;
-        while (cols < 2 * pair_plan.bn) cols *= 2;
-        p.acc_cols = cols;
-        p.to_partial = 0;
-        p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
-        const size_t smem = 1024 + (size_t)pair_plan.stages * (A_STAGE_BYTES + (pair_plan.bn / 2) * BK * 2) +
-                            8 * (2 * pair_plan.stages + 4) + 16;
-        const long long total = (long long)p.tiles_w * p.tiles_t;
-        const int grid = 2 * (int)(total < pairs ? total : pairs);
-        tge_launch_clusters(gemm_tcgen05_pair_kernel, grid, NUM_THREADS, smem, 2, stream, map_w, map_x, p);
-        rc = tge_check_launch("gemm_tcgen05_pair");
-        if (rc != 0) return rc;
-        *splits_out = 0;
-        return 1;
-      }
-    }
+    const int grid = 2 * (int)(total < pairs ? total : pairs);
+    tge_launch_clusters(gemm_tcgen05_pair_kernel, grid, NUM_THREADS, smem, 2, stream, map_w, map_x, p);
+    rc = tge_check_launch("gemm_tcgen05_pair");
+    if (rc != 0) return rc;
+    *splits_out = pair_partial ? pair_plan.splits : 0;
+    return 1;
   }
 
   rc = make_map(&map_x, x, M, K, ldx, plan.bn, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
