@@ -9,7 +9,7 @@
 //   * all 512 tensor-memory columns: two score buffers per query tile (4 x 64) and one output accumulator
 //     per query tile (2 x head size, head size <= 128);
 //   * eight softmax warps (four per query tile, one row per thread), one warp issuing the score
-//     products, one issuing the P V products (one thread issues a tcgen05.mma about every 85 cycles, and
+//     products, one issuing the P V products (one thread, then still chosen by `lane == 0`, issued a tcgen05.mma about every 85 cycles, and
 //     a product of 128 x 64 x 16 keeps the tensor core busy for 32; two issuers gave 58 -> 52 us at 2,048
 //     tokens, a third one nothing), one warp issuing copies; three stages of K and V; P in buffers of its own.
 // While the tensor core adds one tile's P V, the other tile's softmax runs.
