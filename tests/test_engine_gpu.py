@@ -225,6 +225,31 @@ def test_generation_does_not_depend_on_pages_or_budget(model_dirs):
     assert all(o == outputs[0] for o in outputs[1:])
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_many_requests_in_one_step(model_dirs, oracle, name):
+    """150 requests at once in bfloat16: their prompts in one step (450 rows) and then one decoded token each
+    (150 rows, a replayed graph), sizes at which the products pair two SMs on a tile and cut along k."""
+    from aegean_tge_b200 import ops
+    count = 150
+    engine = _engine(model_dirs, name, "bfloat16", max_tokens=count * 64, max_requests=count, max_batch_tokens=512)
+    prompts = [_tokens(name, 3, salt=1000 + i) for i in range(count)]
+    nexts = [_tokens(name, 1, salt=5000 + i) for i in range(count)]
+    first = engine.runner.step([_portion(f"r{i}", prompts[i], [2]) for i in range(count)])
+    for repeat in range(2):      # the second decode step replays the graph the first one captured or warmed
+        second = engine.runner.step([_portion(f"r{i}", nexts[i] if repeat == 0 else [7], [0]) for i in range(count)])
+        if repeat == 0:
+            kept = second.clone()
+    assert first.shape[0] == count and kept.shape[0] == count
+    for i in (0, 1, 63, 64, 127, 128, 149):
+        assert rel_error(first[i], oracle(name, prompts[i])[2]) < MODEL_TOL["bfloat16"], (name, i)
+        assert rel_error(kept[i], oracle(name, prompts[i] + nexts[i])[3]) < MODEL_TOL["bfloat16"], (name, i)
+        assert rel_error(second[i], oracle(name, prompts[i] + nexts[i] + [7])[4]) < MODEL_TOL["bfloat16"], (name, i)
+    ops.check_status()
+    for i in range(count):
+        engine.runner.finish(f"r{i}")
+    engine.cache.check()
+
+
 def test_kernels_are_loaded_and_cpu_is_refused(model_dirs):
     from aegean_tge_b200 import ops
     _engine(model_dirs, "A", "bfloat16")
