@@ -372,3 +372,29 @@ TGE_API int tge_rope_kv_store(void* qkv, int is_bf16, int row_stride, const floa
         (float*)k_pages, (float*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, rotary, store_kv, status);
   return tge_launched("rope_kv_store", 1);
 }
+
+// out[m, n] = rows[m, n] / sqrt(sum over slices of sums[slice][m] / width + eps), bfloat16: completes rows that
+// travelled without their RMSNorm factor, for a taker that cannot apply it itself.
+namespace {
+__global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ rows, long long ld_rows, const float* __restrict__ sums,
+                                  int slices, int width, float eps, __nv_bfloat16* __restrict__ out, long long ld_out,
+                                  int m_rows, int n_cols) {
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x;
+  float sum = 0.0f;
+  for (int slice = 0; slice < slices; ++slice) sum += sums[(size_t)slice * m_rows + m];
+  const float factor = 1.0f / sqrtf(sum / (float)width + eps);
+  for (int n = threadIdx.x; n < n_cols; n += blockDim.x)
+    out[(size_t)m * ld_out + n] = __float2bfloat16_rn(__bfloat162float(rows[(size_t)m * ld_rows + n]) * factor);
+}
+}  // namespace
+
+TGE_API int tge_scale_rows(const void* rows, long long ld_rows, const float* sums, int slices, int width, float eps,
+                           void* out, long long ld_out, int m_rows, int n_cols, cudaStream_t stream) {
+  TGE_REQUIRE(m_rows >= 0 && n_cols > 0 && slices > 0 && width > 0, "scale_rows: bad sizes");
+  if (m_rows == 0) return 0;
+  tge_launch(scale_rows_kernel, m_rows, 256, 0, stream, (const __nv_bfloat16*)rows, ld_rows, sums, slices, width, eps,
+             (__nv_bfloat16*)out, ld_out, m_rows, n_cols);
+  return tge_launched("scale_rows", 1);
+}

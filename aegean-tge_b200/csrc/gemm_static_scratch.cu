@@ -34,6 +34,7 @@
 extern "C" int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias,
                                 void* out, long long ldo, int M, int N, int K, int epilogue, float* scratch,
                                 long long scratch_floats, int force_bn, int force_splits, int* status,
+                                const float* x_ss, int x_ss_slices, int x_ss_width, float x_ss_eps,
                                 cudaStream_t stream);
 extern "C" long long tge_gemm_tcgen05_scratch_floats(int M, int N, int K);
 
@@ -68,5 +69,5 @@ TGE_API int tge_gemm_tcgen05_static_scratch(const void* x, long long ldx, const 
     g_scratch_address[device] = static_cast<float*>(address);
   }
   return tge_gemm_tcgen05(x, ldx, w, ldw, bias, out, ldo, M, N, K, epilogue, g_scratch_address[device],
-                          (long long)TGE_STATIC_SCRATCH_FLOATS, 0, 0, status, stream);
+                          (long long)TGE_STATIC_SCRATCH_FLOATS, 0, 0, status, nullptr, 0, 0, 0.0f, stream);
 }

@@ -55,7 +55,13 @@ struct GemmParams {
   long long ldo;
   float* partial;
   int* status;
+  // Rows of x that still lack their RMSNorm factor: 1 / sqrt(sum over slices of ss[slice][token] / ss_width + ss_eps)
+  // multiplies the product's column of that token (null: x is complete).  At most DEFER_MAX_TOKENS tokens.
+  const float* ss;
+  int ss_slices, ss_width;
+  float ss_eps;
 };
+constexpr int DEFER_MAX_TOKENS = 128;
 
 // ---- PTX wrappers ----------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -147,10 +153,26 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// 1 / sqrt(mean square of the row + eps) from the row's sums of squares in slices (added in slice order; the
+// loads of eight slices are in flight together)
+__device__ __forceinline__ float row_factor_of(const float* __restrict__ ss, int slices, int width, float eps, int m_tok, int m) {
+  if (ss == nullptr) return 1.0f;
+  float sum = 0.0f;
+  for (int first = 0; first < slices; first += 8) {
+    float part[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part[i] = first + i < slices ? ss[(size_t)(first + i) * m_tok + m] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum += part[i];
+  }
+  return 1.0f / sqrtf(sum / (float)width + eps);
+}
+
 // The epilogue of one finished tile: this warp's 32 lanes (weight rows n) by its columns [c_begin, c_end)
 // of the accumulator buffer `acc`.
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_base, int acc, int quarter, int lane,
-                                              int c_begin, int c_end, int n, int tile_t, int split) {
+                                              int c_begin, int c_end, int n, int tile_t, int split,
+                                              const float* row_factor = nullptr) {
   const bool n_ok = n < p.n_w;
   const float bias = (p.bias && n_ok && !p.to_partial) ? p.bias[n] : 0.0f;
   for (int c0 = c_begin; c0 < c_end; c0 += 16) {
@@ -159,6 +181,11 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
     tc_load16(taddr, r);
     const int m0 = tile_t * p.bn + c0;
     if (m0 >= p.m_tok) continue;                              // uniform over the warp
+    if (row_factor != nullptr && !p.to_partial) {             // partial sums stay as they are: who adds them scales
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        r[j] = __float_as_uint(__uint_as_float(r[j]) * row_factor[min(m0 + j, DEFER_MAX_TOKENS - 1)]);
+    }
     if (!p.to_partial && p.epilogue == GEMM_ADD_F32) {
       // read all sixteen old values before the first store, so the loads overlap
       float* dst = reinterpret_cast<float*>(p.out) + (size_t)m0 * p.ldo + n;
@@ -253,6 +280,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   if (warp != 0) pdl_wait();
 
   const int total_work = p.tiles_w * p.tiles_t * p.splits;
+  float* row_factor = nullptr;
+  if (p.ss != nullptr && !p.to_partial && warp >= 2) {
+    // the epilogue warps work out every token's factor once, while the first tile is being multiplied
+    // (partial sums are left unscaled: the kernel that adds them applies the factor)
+    row_factor = reinterpret_cast<float*>(const_cast<int*>(abort_flag) + 3);
+    const int m = (int)threadIdx.x - 64;
+    if (m < DEFER_MAX_TOKENS)
+      row_factor[m] = m < p.m_tok ? row_factor_of(p.ss, p.ss_slices, p.ss_width, p.ss_eps, p.m_tok, m) : 0.0f;
+    asm volatile("bar.sync 1, %0;\n" ::"n"(EPI_WARPS * 32) : "memory");
+  }
 
   if (warp == 0) {
     // ------------------------------ TMA loader ------------------------------
@@ -357,7 +394,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int tile_t = rest % p.tiles_t, tile_w = rest / p.tiles_t;
       if (!mbar_wait(tfull_bar(acc), acc_phase, p.status, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      epilogue_tile(p, tmem_base, acc, quarter, lane, c_begin, c_end, tile_w * BM + quarter * 32 + lane, tile_t, split);
+      epilogue_tile(p, tmem_base, acc, quarter, lane, c_begin, c_end, tile_w * BM + quarter * 32 + lane, tile_t, split,
+                    row_factor);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
@@ -574,7 +612,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 
 // Adds the k-splits in split order and applies the epilogue.
 __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const float* __restrict__ bias, void* out,
-                                       long long ldo, int m_tok, int n_w, int splits, int epilogue) {
+                                       long long ldo, int m_tok, int n_w, int splits, int epilogue,
+                                       const float* __restrict__ ss, int ss_slices, int ss_width, float ss_eps) {
   pdl_trigger();
   pdl_wait();
   const size_t plane = (size_t)m_tok * n_w;
@@ -588,6 +627,9 @@ __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const 
         g += v.x;
         u += v.y;
       }
+      const float factor = row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, m);
+      g *= factor;
+      u *= factor;
       if (bias) { g += bias[2 * c]; u += bias[2 * c + 1]; }
       reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + c] = __float2bfloat16_rn(silu_mul(g, u));
     }
@@ -597,6 +639,7 @@ __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const 
     const int m = (int)(i / n_w), n = (int)(i % n_w);
     float v = 0.0f;
     for (int s = 0; s < splits; ++s) v += partial[s * plane + i];
+    v *= row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, m);
     if (bias) v += bias[n];
     if (epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
     else if (epilogue == GEMM_STORE_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
@@ -658,6 +701,13 @@ int sm_count() {
 
 struct Plan {
   int bn, stages, splits;
+};
+
+// Sums of squares of the rows of x, in slices, when x still lacks its RMSNorm factor (ss null: it does not).
+struct RowSums {
+  const float* ss = nullptr;
+  int slices = 0, width = 0;
+  float eps = 0.0f;
 };
 
 Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int force_splits) {
@@ -843,7 +893,7 @@ namespace {
 int launch_product(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
                    long long ldo, int M, int N, int K, int epilogue, float* scratch, long long scratch_floats,
                    int force_bn, int force_splits, bool partial_always, int* status, cudaStream_t stream,
-                   int* splits_out) {
+                   int* splits_out, const RowSums& sums = RowSums()) {
   if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)w % 16 != 0) return TGE_UNSUPPORTED;
   if (scratch == nullptr) scratch_floats = 0;
   const Plan plan = make_plan(M, N, K, scratch_floats, force_bn, force_splits);
@@ -856,8 +906,10 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   int rc = make_map(&map_w, w, N, K, ldw, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
   if (rc != 0) return rc;
 
+  TGE_REQUIRE(sums.ss == nullptr || (M <= DEFER_MAX_TOKENS && sums.slices > 0 && sums.width > 0),
+              "gemm_tcgen05: rows without their norm factor: at most %d tokens, got %d", DEFER_MAX_TOKENS, M);
   Plan pair_plan;
-  if (choose_pair(M, N, K, scratch_floats, plan, force_bn, force_splits, &pair_plan)) {
+  if (sums.ss == nullptr && choose_pair(M, N, K, scratch_floats, plan, force_bn, force_splits, &pair_plan)) {
     const bool pair_partial = partial_always || pair_plan.splits > 1;
     TGE_REQUIRE(!pair_partial || (long long)pair_plan.splits * M * N <= scratch_floats,
                 "gemm_tcgen05: %d k-splits need %lld floats of scratch, have %lld", pair_plan.splits,
@@ -876,6 +928,7 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
     p.acc_cols = cols;
     p.to_partial = pair_partial ? 1 : 0;
     p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
+    p.ss = nullptr; p.ss_slices = 0; p.ss_width = 0; p.ss_eps = 0.0f;
     const size_t smem = 1024 + (size_t)pair_plan.stages * (A_STAGE_BYTES + (pair_plan.bn / 2) * BK * 2) +
                         8 * (2 * pair_plan.stages + 4) + 16;
     const long long total = (long long)p.tiles_w * p.tiles_t * p.splits;
@@ -903,8 +956,10 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   p.acc_cols = cols;
   p.to_partial = to_partial ? 1 : 0;
   p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
+  p.ss = sums.ss; p.ss_slices = sums.slices; p.ss_width = sums.width; p.ss_eps = sums.eps;
 
-  const size_t smem = 1024 + (size_t)plan.stages * (A_STAGE_BYTES + plan.bn * BK * 2) + 8 * (2 * plan.stages + 4) + 16;
+  const size_t smem = 1024 + (size_t)plan.stages * (A_STAGE_BYTES + plan.bn * BK * 2) + 8 * (2 * plan.stages + 4) + 16 +
+                      DEFER_MAX_TOKENS * sizeof(float);
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
@@ -983,18 +1038,32 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
                                              const int* __restrict__ block_table, int max_pages,
                                              __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
                                              int num_pages, int page_size, int heads, int kv_heads, int head_dim,
-                                             int* status) {
+                                             int* status, const float* __restrict__ ss, int ss_slices, int ss_width,
+                                             float ss_eps) {
   extern __shared__ float head_values[];
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, unit = blockIdx.y;     // unit: query heads, then key heads, then value heads
   const size_t plane = (size_t)m_tok * n_w;
   const int column0 = unit * head_dim;
+  // the first sixteen slices' sums are asked for before the partial sums and used after them: one round trip
+  float early[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) early[i] = (ss != nullptr && i < ss_slices) ? ss[(size_t)i * m_tok + t] : 0.0f;
+  float factor = 1.0f;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     const float* src = partial + (size_t)t * n_w + column0 + d;
     float acc = 0.0f;
 #pragma unroll 4
     for (int s = 0; s < splits; ++s) acc += src[s * plane];
+    if (ss != nullptr && d == (int)threadIdx.x) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) sum += early[i];
+      for (int slice = 16; slice < ss_slices; ++slice) sum += ss[(size_t)slice * m_tok + t];
+      factor = 1.0f / sqrtf(sum / (float)ss_width + ss_eps);
+    }
+    acc *= factor;
     if (bias) acc += bias[column0 + d];
     head_values[d] = acc;
   }
@@ -1032,6 +1101,38 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = __float2bfloat16_rn(rotated(d));
 }
 
+// The same without the norm's factor: the stream takes the sums, the next product's input is stream * weight,
+// and each block leaves the sum of squares of its slice of the row; whoever multiplies that input works the
+// factor out of the slices' sums (always in slice order) and applies it to its result.  No block waits for
+// another, so a row is spread over many SMs: 3 us where the kernel above takes 6.5.
+constexpr int SCALE_SLICE = 256;
+
+__global__ void __launch_bounds__(SCALE_SLICE)
+splitk_add_scale_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ stream,
+                        long long ld_stream, const float* __restrict__ norm_weight, __nv_bfloat16* __restrict__ scaled_out,
+                        long long ld_scaled, float* __restrict__ ss_out, int m_tok, int n_w, int splits) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int t = blockIdx.y, n = blockIdx.x * SCALE_SLICE + threadIdx.x;
+  const bool inside = n < n_w;
+  const float gain = inside ? norm_weight[n] : 0.0f;
+  const float add = (bias && inside) ? bias[n] : 0.0f;
+  pdl_wait();
+  float v = 0.0f;
+  if (inside) {
+    const size_t plane = (size_t)m_tok * n_w;
+    const float* src = partial + (size_t)t * n_w + n;
+    float acc = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) acc += src[s * plane];
+    v = stream[(size_t)t * ld_stream + n] + (acc + add);
+    stream[(size_t)t * ld_stream + n] = v;
+    scaled_out[(size_t)t * ld_scaled + n] = __float2bfloat16_rn(v * gain);
+  }
+  const float sum = block_sum(v * v, scratch);
+  if (threadIdx.x == 0) ss_out[(size_t)blockIdx.x * m_tok + t] = sum;
+}
+
 constexpr int FUSED_MAX_TOKENS = 256;   // above this the product's own epilogue is the better path
 
 }  // namespace
@@ -1041,10 +1142,12 @@ constexpr int FUSED_MAX_TOKENS = 256;   // above this the product's own epilogue
 // elements for split-k partial sums (may be null: no split).  force_bn / force_splits: 0 = automatic.
 // Returns TGE_UNSUPPORTED (and touches nothing) when the shape cannot go through TMA: K not a
 // multiple of 8, misaligned pointers or strides.  The caller then uses the CUDA-core product.
+// x_ss (null, or float32 [x_ss_slices, M]): the rows of x still lack their RMSNorm factor
+// 1 / sqrt(sum over slices / x_ss_width + x_ss_eps), which then multiplies the product before the bias.
 TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
                              long long ldo, int M, int N, int K, int epilogue, float* scratch,
                              long long scratch_floats, int force_bn, int force_splits, int* status,
-                             cudaStream_t stream) {
+                             const float* x_ss, int x_ss_slices, int x_ss_width, float x_ss_eps, cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_SWIGLU, "gemm: unknown epilogue %d", epilogue);
   TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
@@ -1052,17 +1155,43 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
   TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
   if (M == 0) return 0;
   int splits = 0;
+  RowSums sums;
+  sums.ss = x_ss; sums.slices = x_ss_slices; sums.width = x_ss_width; sums.eps = x_ss_eps;
   int rc = launch_product(x, ldx, w, ldw, bias, out, ldo, M, N, K, epilogue, scratch, scratch_floats, force_bn,
-                          force_splits, false, status, stream, &splits);
+                          force_splits, false, status, stream, &splits, sums);
   if (rc != 1) return rc;
   if (splits > 0) {
     const long long count = epilogue == GEMM_SWIGLU ? (long long)M * N / 2 : (long long)M * N;
     long long blocks = (count + 255) / 256;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
-    tge_launch(splitk_epilogue_kernel, (int)blocks, 256, 0, stream, (const float*)scratch, bias, out, ldo, M, N, splits, epilogue);
+    tge_launch(splitk_epilogue_kernel, (int)blocks, 256, 0, stream, (const float*)scratch, bias, out, ldo, M, N, splits,
+               epilogue, x_ss, x_ss_slices, x_ss_width, x_ss_eps);
     return tge_launched("splitk_epilogue", 2);
   }
   return 1;
+}
+
+// As tge_gemm_tcgen05_add_norm below, but the norm's factor is left to whoever multiplies the result next:
+// stream [M, N] float32 += x . w^T (+ bias); scaled_out [M, N] bf16 = stream * norm_weight;
+// ss_out float32 [tge_gemm_tcgen05_defer_slices(N), M] = the rows' sums of squares, in slices.  At most 128 tokens.
+TGE_API int tge_gemm_tcgen05_defer_slices(int N) { return (N + SCALE_SLICE - 1) / SCALE_SLICE; }
+
+TGE_API int tge_gemm_tcgen05_add_defer(const void* x, long long ldx, const void* w, long long ldw, const float* bias,
+                                       float* stream_out, long long ldo, int M, int N, int K, const float* norm_weight,
+                                       void* scaled_out, long long ld_scaled, float* ss_out, float* scratch,
+                                       long long scratch_floats, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+defer: bad sizes M=%d N=%d K=%d", M, N, K);
+  TGE_REQUIRE(status != nullptr && norm_weight != nullptr && scaled_out != nullptr && ss_out != nullptr, "gemm+defer: bad arguments");
+  if (M == 0) return 0;
+  if (M > DEFER_MAX_TOKENS || scratch == nullptr) return TGE_UNSUPPORTED;
+  int splits = 0;
+  int rc = launch_product(x, ldx, w, ldw, nullptr, stream_out, ldo, M, N, K, GEMM_ADD_F32, scratch, scratch_floats, 0, 0,
+                          true, status, stream, &splits);
+  if (rc != 1) return rc;
+  tge_launch(splitk_add_scale_kernel, dim3((N + SCALE_SLICE - 1) / SCALE_SLICE, M), SCALE_SLICE, 0, stream,
+             (const float*)scratch, bias, stream_out, ldo, norm_weight, (__nv_bfloat16*)scaled_out, ld_scaled, ss_out, M, N,
+             splits);
+  return tge_launched("splitk_add_scale", 2);
 }
 
 // stream [M, N] float32 += x . w^T (+ bias), then norm_out [M, N] bf16 = RMSNorm(stream rows) * norm_weight:
@@ -1096,6 +1225,7 @@ TGE_API int tge_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* 
                                       const int* seq_of_token, const int* block_table, int max_pages, void* k_pages,
                                       void* v_pages, int num_pages, int page_size, int heads, int kv_heads,
                                       int head_dim, float* scratch, long long scratch_floats, int* status,
+                                      const float* x_ss, int x_ss_slices, int x_ss_width, float x_ss_eps,
                                       cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+rope: bad sizes M=%d N=%d K=%d", M, N, K);
   TGE_REQUIRE(N == (heads + 2 * kv_heads) * head_dim, "gemm+rope: %d weight rows are not (heads + 2 kv heads) * head_dim", N);
@@ -1110,6 +1240,7 @@ TGE_API int tge_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* 
   tge_launch(splitk_qkv_rope_store_kernel, dim3(M, heads + 2 * kv_heads), head_dim >= 128 ? 128 : 64,
              (size_t)head_dim * sizeof(float), stream, (const float*)scratch, bias, (__nv_bfloat16*)qkv, ld_qkv, M, N,
              splits, cos_table, sin_table, table_rows, rotary, positions, seq_of_token, block_table, max_pages,
-             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, status);
+             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, status,
+             x_ss, x_ss_slices, x_ss_width, x_ss_eps);
   return tge_launched("splitk_qkv_rope_store", 2);
 }

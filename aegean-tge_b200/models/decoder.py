@@ -111,8 +111,12 @@ class DecoderModel:
         schedule = self.spec.schedule
         h = None                              # the next layer's first norm, when the previous layer produced it
         for step, index in enumerate(schedule):
-            following = self.blocks[schedule[step + 1]].mixer_norm if step + 1 < len(schedule) else None
-            h = self.blocks[index].forward(x, ctx, self.layer_caches[index], h=h, next_norm=following)
+            after = self.blocks[schedule[step + 1]] if step + 1 < len(schedule) else None
+            following = after.mixer_norm if after is not None else None
+            block = self.blocks[index]
+            more = ({"next_takes_deferred": after is not None and after.mixer.takes_deferred_rows}
+                    if block.passes_deferred_rows else {})
+            h = block.forward(x, ctx, self.layer_caches[index], h=h, next_norm=following, **more)
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         h = self.final_norm.forward(x, rows=logit_rows)

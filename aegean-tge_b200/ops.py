@@ -66,14 +66,21 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_gemm_simt", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
                                         _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
-                                           _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ptr])
+                                           _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
+                                           _c_int, _c_float, _c_ptr])
+        _declare(lib, "tge_gemm_tcgen05_add_defer", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int,
+                                                     _c_int, _c_int, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll,
+                                                     _c_ptr, _c_ptr])
+        _declare(lib, "tge_gemm_tcgen05_defer_slices", [_c_int])
+        _declare(lib, "tge_scale_rows", [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_float, _c_ptr, _c_ll, _c_int,
+                                         _c_int, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05_add_norm", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                                                     _c_int, _c_ptr, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr,
                                                     _c_ptr])
         _declare(lib, "tge_gemm_tcgen05_qkv_rope", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                    _c_ptr, _c_ll, _c_ptr, _c_ptr])
+                                                    _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr])
         lib.tge_gemm_tcgen05_pair_mode.argtypes = [_c_int]
         lib.tge_gemm_tcgen05_pair_mode.restype = None
         lib.tge_gemm_tcgen05_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
@@ -291,6 +298,47 @@ def rope_kv_store(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[
                                  status_word().data_ptr(), _stream()), lib)
 
 
+DEFER_MAX_TOKENS = 128      # rows that may travel without their norm factor (the small-batch products)
+
+
+class DeferredRows:
+    """Rows ``stream * norm_weight`` in bfloat16 that still lack their RMSNorm factor.
+
+    ``sums`` (float32 [slices, M]) holds each row's sum of squares in slices; the factor of row m is
+    ``1 / sqrt(sum over slices / width + eps)``.  The product that takes these rows multiplies its result
+    by it (``linear`` and ``linear_qkv_rope_store`` do); ``complete()`` gives the normalised rows.
+    """
+
+    def __init__(self, rows: torch.Tensor, sums: torch.Tensor, width: int, eps: float):
+        self.rows, self.sums, self.width, self.eps = rows, sums, int(width), float(eps)
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+    @property
+    def device(self):
+        return self.rows.device
+
+    def factor_args(self):
+        return self.sums.data_ptr(), self.sums.shape[0], self.width, self.eps
+
+    def complete(self) -> torch.Tensor:
+        lib = core()
+        M, N = self.rows.shape
+        out = torch.empty_like(self.rows)
+        _check(lib.tge_scale_rows(self.rows.data_ptr(), _rows_2d(self.rows, "rows"), self.sums.data_ptr(),
+                                  self.sums.shape[0], self.width, self.eps, out.data_ptr(), N, M, N, _stream()), lib)
+        return out
+
+
+_NO_FACTOR = (None, 0, 0, 0.0)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
            out: Optional[torch.Tensor] = None, force_simt: bool = False, force_bn: int = 0,
            force_splits: int = 0) -> torch.Tensor:
@@ -303,6 +351,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
     bfloat16 goes to the tcgen05 kernel when the shape allows TMA, else (and all of
     float32) to the CUDA-core kernel.
     """
+    deferred = x if isinstance(x, DeferredRows) else None
+    if deferred is not None:
+        x = deferred.rows
     _want(x, "linear input", _FLOAT, contiguous=False)
     _want(w, "linear weight", x.dtype, contiguous=False)
     ldx, ldw = _rows_2d(x, "linear input"), _rows_2d(w, "linear weight")
@@ -333,14 +384,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
         raise KernelError(f"linear: output must be {want_shape}, got {tuple(out.shape)}")
     ldo = _rows_2d(out, "linear output")
     lib = core()
-    if x.dtype == torch.bfloat16 and USE_TCGEN05 and not force_simt:
+    if x.dtype == torch.bfloat16 and USE_TCGEN05 and not force_simt and (deferred is None or M <= DEFER_MAX_TOKENS):
         need = lib.tge_gemm_tcgen05_scratch_floats(M, N, K) if force_splits == 0 else force_splits * M * N
         scratch = scratch_floats(need) if need > 0 else None
+        factor = _NO_FACTOR if deferred is None else deferred.factor_args()
         rc = lib.tge_gemm_tcgen05(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                                   epilogue, _ptr(scratch), 0 if scratch is None else scratch.numel(), force_bn,
-                                  force_splits, status_word().data_ptr(), _stream())
+                                  force_splits, status_word().data_ptr(), *factor, _stream())
         if _check(rc, lib) != UNSUPPORTED:
             return out
+    if deferred is not None:
+        x = deferred.complete()
+        ldx = _rows_2d(x, "linear input")
     _check(lib.tge_gemm_simt(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                              int(x.dtype == torch.bfloat16), epilogue, _stream()), lib)
     return out
@@ -356,11 +411,13 @@ FUSED_MAX_TOKENS = 256      # small batches: product + one kernel per token row;
 
 
 def linear_add_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], stream: torch.Tensor,
-                    norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+                    norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype, defer: bool = False):
     """stream (float32 [M, N]) += x . w^T (+ bias); returns RMSNorm(stream) * norm_weight in ``out_dtype``.
 
     For a small bfloat16 batch the partial sums of the product are added into the stream and the new
     rows normalised by one kernel; otherwise the product and the norm run as separate kernels.
+    With ``defer`` (the caller knows that ``linear`` or ``linear_qkv_rope_store`` takes the result) up to 128
+    rows may come back as :class:`DeferredRows`: without the norm's factor, which their taker applies.
     """
     M, K = x.shape
     N = w.shape[0]
@@ -377,6 +434,16 @@ def linear_add_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tenso
         need = max(lib.tge_gemm_tcgen05_scratch_floats(M, N, K), M * N)
         scratch = scratch_floats(need)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        if defer and M <= DEFER_MAX_TOKENS and N % 8 == 0:
+            # the taker of these rows applies the norm's factor: no block waits for a whole row here
+            sums = torch.empty((lib.tge_gemm_tcgen05_defer_slices(N), M), dtype=torch.float32, device=x.device)
+            rc = lib.tge_gemm_tcgen05_add_defer(x.data_ptr(), _rows_2d(x, "linear input"), w.data_ptr(),
+                                                _rows_2d(w, "linear weight"), _ptr(bias), stream.data_ptr(),
+                                                _rows_2d(stream, "stream"), M, N, K, norm_weight.data_ptr(),
+                                                out.data_ptr(), N, sums.data_ptr(), scratch.data_ptr(),
+                                                scratch.numel(), status_word().data_ptr(), _stream())
+            if _check(rc, lib) != UNSUPPORTED:
+                return DeferredRows(out, sums, N, eps)
         rc = lib.tge_gemm_tcgen05_add_norm(x.data_ptr(), _rows_2d(x, "linear input"), w.data_ptr(),
                                            _rows_2d(w, "linear weight"), _ptr(bias), stream.data_ptr(),
                                            _rows_2d(stream, "stream"), M, N, K, norm_weight.data_ptr(), float(eps),
@@ -399,6 +466,9 @@ def linear_qkv_rope_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch
     rotates and stores; otherwise the product and the rotate-and-store kernel run one after the other
     (then the k and v columns of the buffer are filled as well).
     """
+    deferred = x if isinstance(x, DeferredRows) else None
+    if deferred is not None:
+        x = deferred.rows
     M, K = x.shape
     N = w.shape[0]
     if (x.dtype == torch.bfloat16 and USE_TCGEN05 and M <= FUSED_MAX_TOKENS):
@@ -426,10 +496,11 @@ def linear_qkv_rope_store(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch
                                            positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
                                            block_table.shape[1], k_pages.data_ptr(), v_pages.data_ptr(), num_pages,
                                            page_size, heads, kv_heads, head_dim, scratch.data_ptr(), scratch.numel(),
-                                           status_word().data_ptr(), _stream())
+                                           status_word().data_ptr(),
+                                           *(_NO_FACTOR if deferred is None else deferred.factor_args()), _stream())
         if _check(rc, lib) != UNSUPPORTED:
             return qkv
-    qkv = linear(x, w, bias, GEMM_STORE)
+    qkv = linear(x if deferred is None else deferred, w, bias, GEMM_STORE)
     rope_kv_store(qkv, cos, sin, rotary, positions, seq_of_token, block_table, k_pages, v_pages, heads, kv_heads,
                   head_dim)
     return qkv

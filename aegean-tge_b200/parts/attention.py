@@ -28,6 +28,8 @@ class GQAttention(Mixer):
     weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``.
     """
     graph_safe = True
+    can_defer_norm = True
+    takes_deferred_rows = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -125,10 +127,11 @@ class GQAttention(Mixer):
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         return self.ops.linear(self.attend(h, ctx, cache), self.w_o, self.b_o, self.ops.GEMM_STORE)
 
-    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache, next_norm=None):
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache, next_norm=None,
+                    defer: bool = False):
         a = self.attend(h, ctx, cache)
         fused = next_norm.fusable() if next_norm is not None else None
         if fused is not None:
-            return self.ops.linear_add_norm(a, self.w_o, self.b_o, x, fused[0], fused[1], self.env.dtype)
+            return self.ops.linear_add_norm(a, self.w_o, self.b_o, x, fused[0], fused[1], self.env.dtype, defer=defer)
         self.ops.linear(a, self.w_o, self.b_o, self.ops.GEMM_ADD_F32, out=x)
         return None

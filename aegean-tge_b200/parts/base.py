@@ -130,6 +130,13 @@ class Part:
     # Steps of single tokens are then captured once into a CUDA graph and replayed; one part that leaves
     # this False makes the whole model run eagerly.
     graph_safe = False
+    # Rows that a fused product and norm hands on may lack the norm's factor (``ops.DeferredRows``), which
+    # saves the kernel that makes them a whole-row reduction.  A mixer or feed-forward whose ``forward_add``
+    # accepts ``defer=True`` and passes it to ``ops.linear_add_norm`` sets ``can_defer_norm``; one whose first
+    # use of ``h`` is ``ops.linear`` or ``ops.linear_qkv_rope_store`` (which apply the factor) sets
+    # ``takes_deferred_rows``.  Both False: the part only ever sees plain tensors.
+    can_defer_norm = False
+    takes_deferred_rows = False
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec
@@ -229,9 +236,13 @@ class Block:
         """Runs the layer on the stream ``x`` in place.
 
         ``h``: ``mixer_norm(x)`` if the previous layer already computed it.  ``next_norm``: the norm the
-        next layer will apply to ``x`` first; the block may return its result (else None).
+        next layer will apply to ``x`` first; the block may return its result (else None).  A block that
+        sets ``passes_deferred_rows`` is also given ``next_takes_deferred``: whether the next layer's mixer
+        takes rows without their norm factor.
         """
         raise NotImplementedError
+
+    passes_deferred_rows = False
 
     def parts(self) -> Dict[str, Part]:
         return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,

@@ -15,10 +15,15 @@ class PreNormBlock(Block):
     (src/models/qwen2.cpp:2055, :2099-2105, :2118).
     """
 
-    def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None):
+    passes_deferred_rows = True
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None, next_takes_deferred=False):
         if h is None:
             h = self.mixer_norm.forward(x)
-        h = self.mixer.forward_add(h, x, ctx, cache, next_norm=self.ffn_norm)
+        # a part is only asked to leave the norm's factor to its successor if both sides say they can
+        defer = {"defer": True} if self.mixer.can_defer_norm and self.feed_forward.takes_deferred_rows else {}
+        h = self.mixer.forward_add(h, x, ctx, cache, next_norm=self.ffn_norm, **defer)
         if h is None:
             h = self.ffn_norm.forward(x)
-        return self.feed_forward.forward_add(h, x, ctx, next_norm=next_norm)
+        defer = {"defer": True} if self.feed_forward.can_defer_norm and next_takes_deferred else {}
+        return self.feed_forward.forward_add(h, x, ctx, next_norm=next_norm, **defer)

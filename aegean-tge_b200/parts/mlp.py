@@ -19,6 +19,8 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec, StepContext
 class SwiGLU(FeedForward):
     """params: ``hidden_size``, ``intermediate_size``.  weights: ``gate|up|down.weight``."""
     graph_safe = True
+    can_defer_norm = True
+    takes_deferred_rows = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -48,10 +50,10 @@ class SwiGLU(FeedForward):
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
         return self.ops.linear(a, self.w_down, None, self.ops.GEMM_STORE)
 
-    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None):
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None, defer: bool = False):
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
         fused = next_norm.fusable() if next_norm is not None else None
         if fused is not None:
-            return self.ops.linear_add_norm(a, self.w_down, None, x, fused[0], fused[1], self.env.dtype)
+            return self.ops.linear_add_norm(a, self.w_down, None, x, fused[0], fused[1], self.env.dtype, defer=defer)
         self.ops.linear(a, self.w_down, None, self.ops.GEMM_ADD_F32, out=x)
         return None

@@ -206,6 +206,40 @@ def test_gemm_pair_epilogues(ops, pair_everywhere, M, N, K):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 3584, 512), (33, 520, 264), (128, 1024, 320), (150, 384, 192)])
+@pytest.mark.parametrize("defer", [False, True])
+def test_linear_add_norm_and_rows_without_their_factor(ops, M, N, K, defer):
+    """stream += x . w^T; the next product's input = RMSNorm(stream) * weight, either complete or (up to 128
+    rows, if asked) without the norm's factor, which the product that takes the rows then applies: with a bias,
+    with the gated epilogue, cut along k or not, and completed on their own."""
+    gen = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=gen) * 0.1).to(torch.bfloat16)
+    stream = torch.randn(M, N, generator=gen) * 3.0
+    gain = 1.0 + 0.2 * torch.randn(N, generator=gen)
+    eps = 1e-5
+    new_stream = stream.double() + ops_plain.linear(x, w, None)
+    normed = ops_plain.rmsnorm(new_stream, gain, eps)
+    d_stream = stream.to(DEV)
+    rows = ops.linear_add_norm(x.to(DEV), w.to(DEV), None, d_stream, gain.to(DEV), eps, torch.bfloat16, defer=defer)
+    assert rel_error(d_stream, new_stream) < 2e-5
+    assert isinstance(rows, ops.DeferredRows) == (defer and M <= 128)
+    if isinstance(rows, ops.DeferredRows):
+        assert rel_error(rows.complete(), normed) < 2 * TOL[torch.bfloat16]
+    else:
+        assert rel_error(rows, normed) < TOL[torch.bfloat16]
+    # takers: a plain product with a bias (few weight rows and a long k: cut along k) and a gated one
+    for rows_out, k_cut in ((40, True), (768, False)):
+        w2 = (torch.randn(rows_out, N, generator=gen) * 0.05).to(torch.bfloat16)
+        b2 = torch.randn(rows_out, generator=gen)
+        want = ops_plain.linear(normed, w2, b2)
+        got = ops.linear(rows, w2.to(DEV), b2.to(DEV), ops.GEMM_STORE_F32)
+        assert rel_error(got, want) < TOL[torch.bfloat16], (rows_out, k_cut)
+        got = ops.linear(rows, w2.to(DEV), None, ops.GEMM_SWIGLU)
+        assert rel_error(got, ops_plain.swiglu_interleaved(normed, w2)) < 2 * TOL[torch.bfloat16]
+    ops.check_status()
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_address(ops):
     """K that is no multiple of 8 cannot be a TMA row pitch: the product still comes out right (CUDA cores)."""
     gen = torch.Generator().manual_seed(11)
