@@ -594,7 +594,6 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ unsigned char smem_dyn[];
   pdl_trigger();
-  pdl_wait();
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzle atoms are 1024 bytes
   unsigned char* generic = smem_dyn + (base - raw);
@@ -638,6 +637,10 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   }
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // the cleared stages, before TMA writes them
   __syncthreads();
+  // All of the above read only what the step was given (lengths, the block table), which no kernel of the step
+  // writes: it ran while the kernel before this one finished.  The queries and the newest keys and values are
+  // that kernel's work.
+  pdl_wait();
 
   const int pages_per_tile = BKV >> p.page_shift;
   auto issue = [&](int tile) {                                          // the loading warp's first lane only
@@ -1154,30 +1157,33 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
                                        int out_stride, int total_tokens, int heads, int window, int split_tokens,
                                        int num_splits) {
   pdl_trigger();
-  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
-  const int pos = positions[t];
-  const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
-  const int s_lo = first_key / split_tokens;
-  const int s_hi = min(pos / split_tokens, num_splits - 1);
+  const int pos = positions[t];                                     // given to the step: not the previous kernel's work
+  pdl_wait();
   const size_t stride = (size_t)total_tokens * heads;               // slots per split
   const size_t slot0 = (size_t)t * heads + h;
   constexpr int HELD = 16;                                          // splits whose state is held in registers
-  if (s_hi - s_lo < HELD) {
-    // every load is asked for before the first result is needed: one round trip instead of three
+  if (num_splits <= HELD) {
+    // Every load is asked for before the first result is needed, the row's position among them: one round
+    // trip instead of four.  Splits without a key visible to the row are read too (the scratch holds all
+    // splits; what lies there is old) and dropped by selection, never by a weight of zero.
     float2 ml[HELD];
 #pragma unroll
-    for (int i = 0; i < HELD; ++i) {
-      const int s = s_lo + i;
-      ml[i] = s <= s_hi ? *reinterpret_cast<const float2*>(partial_ml + ((size_t)s * stride + slot0) * 2)
-                        : make_float2(-INFINITY, 0.0f);
-    }
+    for (int i = 0; i < HELD; ++i)
+      ml[i] = i < num_splits ? *reinterpret_cast<const float2*>(partial_ml + ((size_t)i * stride + slot0) * 2)
+                             : make_float2(-INFINITY, 0.0f);
+    const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
+    const int s_lo = first_key / split_tokens;
+    const int s_hi = min(pos / split_tokens, num_splits - 1);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
       float o[HELD];
 #pragma unroll
+      for (int i = 0; i < HELD; ++i) o[i] = i < num_splits ? partial_o[((size_t)i * stride + slot0) * HD + d] : 0.0f;
+#pragma unroll
       for (int i = 0; i < HELD; ++i) {
-        const int s = s_lo + i;
-        o[i] = s <= s_hi ? partial_o[((size_t)s * stride + slot0) * HD + d] : 0.0f;
+        const bool live = i >= s_lo && i <= s_hi;
+        ml[i] = live ? ml[i] : make_float2(-INFINITY, 0.0f);
+        o[i] = live ? o[i] : 0.0f;
       }
       float m = -INFINITY;
 #pragma unroll
@@ -1194,6 +1200,9 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
     }
     return;
   }
+  const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
+  const int s_lo = first_key / split_tokens;
+  const int s_hi = min(pos / split_tokens, num_splits - 1);
   float m = -INFINITY;
   for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, partial_ml[((size_t)s * stride + slot0) * 2]);
   const float m_use = m == -INFINITY ? 0.0f : m;

@@ -1042,10 +1042,35 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
                                              float ss_eps) {
   extern __shared__ float head_values[];
   pdl_trigger();
-  pdl_wait();
   const int t = blockIdx.x, unit = blockIdx.y;     // unit: query heads, then key heads, then value heads
   const size_t plane = (size_t)m_tok * n_w;
   const int column0 = unit * head_dim;
+  // What the step was given and the model's constants are read while the product before this kernel still
+  // runs: the position and its angles, the page; only the partial sums (and the sums of squares) are its work.
+  const int pos = positions[t];
+  const int half = rotary / 2;
+  const bool is_value = unit >= heads + kv_heads;
+  const bool pos_ok = is_value || half == 0 || (pos >= 0 && pos < table_rows);
+  int page = 0, page_index = 0;
+  if (unit >= heads) {
+    const int seq = seq_of_token[t];
+    page_index = pos / page_size;
+    page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
+  }
+  // the angle of every dimension this thread will write (two dimensions per thread at most: head sizes up to 256)
+  float angle_cos[2] = {1.0f, 1.0f}, angle_sin[2] = {0.0f, 0.0f};
+  if (!is_value && pos_ok) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int d = (int)threadIdx.x + i * (int)blockDim.x;
+      if (d < rotary) {
+        const int j = d < half ? d : d - half;
+        angle_cos[i] = cos_table[(size_t)pos * half + j];
+        angle_sin[i] = sin_table[(size_t)pos * half + j];
+      }
+    }
+  }
+  pdl_wait();
   // the first sixteen slices' sums are asked for before the partial sums and used after them: one round trip
   float early[16];
 #pragma unroll
@@ -1068,43 +1093,38 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
     head_values[d] = acc;
   }
   __syncthreads();
-  const int pos = positions[t];
-  const int half = rotary / 2;
-  const bool is_value = unit >= heads + kv_heads;
-  if (!is_value && half > 0 && (pos < 0 || pos >= table_rows)) {
+  if (!pos_ok) {
     if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
     return;
   }
-  const float* cs = cos_table + (size_t)pos * half;
-  const float* sn = sin_table + (size_t)pos * half;
-  auto rotated = [&](int d) -> float {
-    if (is_value) return head_values[d];
-    if (d < half) return head_values[d] * cs[d] - head_values[d + half] * sn[d];
-    if (d < rotary) return head_values[d - half] * sn[d - half] + head_values[d] * cs[d - half];
-    return head_values[d];
+  auto rotated = [&](int d, int i) -> float {
+    if (is_value || d >= rotary) return head_values[d];
+    if (d < half) return head_values[d] * angle_cos[i] - head_values[d + half] * angle_sin[i];
+    return head_values[d - half] * angle_sin[i] + head_values[d] * angle_cos[i];
   };
+  __nv_bfloat16* dst;
   if (unit < heads) {
-    __nv_bfloat16* dst = qkv + (size_t)t * ld_qkv + column0;
-    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = __float2bfloat16_rn(rotated(d));
-    return;
+    dst = qkv + (size_t)t * ld_qkv + column0;
+  } else {
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+      return;
+    }
+    const int h = is_value ? unit - heads - kv_heads : unit - heads;
+    dst = (is_value ? v_pages : k_pages) +
+          (((size_t)page * kv_heads + h) * page_size + (pos - page_index * page_size)) * head_dim;
   }
-  const int seq = seq_of_token[t];
-  const int page_index = pos / page_size;
-  const int page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
-  if (page < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
-    return;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int d = (int)threadIdx.x + i * (int)blockDim.x;
+    if (d < head_dim) dst[d] = __float2bfloat16_rn(rotated(d, i));
   }
-  const int h = is_value ? unit - heads - kv_heads : unit - heads;
-  __nv_bfloat16* dst = (is_value ? v_pages : k_pages) +
-                       (((size_t)page * kv_heads + h) * page_size + (pos - page_index * page_size)) * head_dim;
-  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) dst[d] = __float2bfloat16_rn(rotated(d));
 }
 
-// The same without the norm's factor: the stream takes the sums, the next product's input is stream * weight,
-// and each block leaves the sum of squares of its slice of the row; whoever multiplies that input works the
-// factor out of the slices' sums (always in slice order) and applies it to its result.  No block waits for
-// another, so a row is spread over many SMs: 3 us where the kernel above takes 6.5.
+// The add+norm kernel without the norm's factor: the stream takes the sums, the next product's input is
+// stream * weight, and each block leaves the sum of squares of its slice of the row; whoever multiplies that
+// input works the factor out of the slices' sums (always in slice order) and applies it to its result.  No
+// block waits for another, so a row is spread over many SMs: 4 us in a step where the kernel above takes 7.
 constexpr int SCALE_SLICE = 256;
 
 __global__ void __launch_bounds__(SCALE_SLICE)
