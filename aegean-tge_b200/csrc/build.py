@@ -30,10 +30,10 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 CORE_SOURCES = ["host_util.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "attention_simt.cu", "sampling.cu", "sampling_cuts.cu",
-                "gemm_static_scratch.cu"]
-HEADERS = ["common.cuh", "gemm_static_scratch.h", "attention_tc.cuh", "attention_tc2.cuh"]
+                "gemm_static_scratch.cu", "random_fill.cu"]
+HEADERS = ["common.cuh", "gemm_static_scratch.h", "random_weights.h", "attention_tc.cuh", "attention_tc2.cuh"]
 RUNTIME_SOURCES = ["runtime.cpp"]
-RUNTIME_HEADERS = ["runtime.h"]
+RUNTIME_HEADERS = ["runtime.h", "random_weights.h"]
 
 
 class BuildError(RuntimeError):
@@ -152,7 +152,7 @@ def build_runtime() -> str:
     out_dir = build_dir()
     lib_path = os.path.join(out_dir, "libtge_runtime.so")
     stamp_path = lib_path + ".hash"
-    flags = ["-O2", "-std=c++17", "-fPIC", "-shared"]
+    flags = ["-O2", "-std=c++17", "-fPIC", "-shared", "-pthread"]
     wanted = _hash(RUNTIME_SOURCES, flags, RUNTIME_HEADERS)
 
     def fresh() -> bool:
@@ -173,7 +173,7 @@ def build_runtime() -> str:
             _log(f"building libtge_runtime.so with {compiler[0]}")
             tmp_path = lib_path + f".tmp{os.getpid()}"
             if os.path.basename(compiler[0]).startswith("nvcc"):
-                cmd = [*compiler, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared"]
+                cmd = [*compiler, "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread", "-shared"]
             else:
                 cmd = [*compiler, *flags]
             cmd += [os.path.join(CSRC, name) for name in RUNTIME_SOURCES] + ["-o", tmp_path]

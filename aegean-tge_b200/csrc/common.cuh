@@ -64,6 +64,8 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ int uniform_warp_index() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
 
 bool tge_pdl_enabled();
+// Streaming multiprocessors of the current device (asked once).
+int tge_sm_count();
 
 // Launches `kernel` so that it may start while its predecessor in the stream drains (see above).
 template <typename... KernelArgs, typename... Args>

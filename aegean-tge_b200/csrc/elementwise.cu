@@ -164,7 +164,7 @@ TGE_API int tge_add_to_stream(float* x, const void* y, int y_is_bf16, long long 
   TGE_REQUIRE(count >= 0, "add_to_stream: negative count");
   if (count == 0) return 0;
   long long blocks = (count + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > tge_sm_count() * 16) blocks = tge_sm_count() * 16;
   if (y_is_bf16)
     add_to_stream_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)y, (size_t)count);
   else

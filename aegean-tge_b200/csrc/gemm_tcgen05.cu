@@ -688,16 +688,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
   return 0;
 }
 
-int sm_count() {
-  static int count = 0;
-  if (count == 0) {
-    int device = 0;
-    cudaGetDevice(&device);
-    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
-    if (count <= 0) count = 1;
-  }
-  return count;
-}
+int sm_count() { return tge_sm_count(); }
 
 struct Plan {
   int bn, stages, splits;

@@ -34,6 +34,19 @@ bool tge_pdl_enabled() {
   return enabled == 1;
 }
 
+int tge_sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 1;
+  }
+  return count;
+}
+
+TGE_API int tge_device_sm_count() { return tge_sm_count(); }
+
 TGE_API const char* tge_last_error() { return g_error; }
 
 TGE_API int tge_abi_version() { return 1; }

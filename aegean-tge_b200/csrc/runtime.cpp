@@ -8,7 +8,11 @@
 // admission by free pages, and preemption with recompute when pages run out.
 #include "runtime.h"
 
+#include "random_weights.h"
+
 #include <algorithm>
+#include <cstring>
+#include <thread>
 #include <cstdarg>
 #include <cstdio>
 #include <deque>
@@ -757,5 +761,57 @@ int tge_rt_sched_forget(TgeRtScheduler* s, int64_t request) {
   return 0;
 }
 long long tge_rt_sched_counter(const TgeRtScheduler* s, int which) { return which >= 0 && which < 5 ? s->counters[which] : -1; }
+
+
+// ------------------------------------------------------------------------------------------------------
+// random weights on the host
+namespace {
+
+inline uint16_t bf16_round_nearest_even(float value) {
+  uint32_t bits;
+  std::memcpy(&bits, &value, 4);
+  if ((bits & 0x7F800000u) == 0x7F800000u && (bits & 0x007FFFFFu)) return (uint16_t)((bits >> 16) | 0x0040u);   // NaN
+  bits += 0x7FFFu + ((bits >> 16) & 1u);
+  return (uint16_t)(bits >> 16);
+}
+
+void random_fill_range(void* out, int is_bf16, long long begin, long long end, long long first, uint64_t key, int kind,
+                       float scale, int base, uint32_t span) {
+  for (long long i = begin; i < end; ++i) {
+    const uint64_t index = (uint64_t)(first + i);
+    // one int-to-float conversion and one multiplication, each rounded once: nothing for a compiler to contract
+    const float value = kind == TGE_RANDOM_NORMAL ? (float)tge_rw_normal_int(key, index)
+                                                     : (float)tge_rw_uniform_int(key, index, base, span);
+    const float result = value * (kind == TGE_RANDOM_NORMAL ? scale : 5.9604644775390625e-08f);
+    if (is_bf16)
+      static_cast<uint16_t*>(out)[i] = bf16_round_nearest_even(result);
+    else
+      static_cast<float*>(out)[i] = result;
+  }
+}
+
+}  // namespace
+
+int tge_rt_random_fill(void* out, int is_bf16, long long count, long long first, unsigned long long key, int kind,
+                       float scale, int base, unsigned int span, int threads) {
+  if (count < 0 || first < 0) return fail(TGE_RT_VALUE_ERROR, "random_fill: bad range first=%lld count=%lld", first, count);
+  if (kind != TGE_RANDOM_NORMAL && kind != TGE_RANDOM_UNIFORM) return fail(TGE_RT_VALUE_ERROR, "random_fill: unknown kind %d", kind);
+  if (out == nullptr && count > 0) return fail(TGE_RT_VALUE_ERROR, "random_fill: no output buffer");
+  const long long grain = 1 << 16;
+  int workers = (int)std::min<long long>(std::max(threads, 1), (count + grain - 1) / grain);
+  if (workers <= 1) {
+    random_fill_range(out, is_bf16, 0, count, first, key, kind, scale, base, span);
+    return 0;
+  }
+  std::vector<std::thread> pool;
+  const long long share = (count + workers - 1) / workers;
+  for (int w = 0; w < workers; ++w) {
+    const long long begin = w * share, end = std::min(count, begin + share);
+    if (begin >= end) break;
+    pool.emplace_back(random_fill_range, out, is_bf16, begin, end, first, (uint64_t)key, kind, scale, base, (uint32_t)span);
+  }
+  for (std::thread& t : pool) t.join();
+  return 0;
+}
 
 }  // extern "C"

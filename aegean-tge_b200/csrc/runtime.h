@@ -115,6 +115,13 @@ int tge_rt_sched_tokens(const TgeRtScheduler* s, int64_t request, int start, int
 int tge_rt_sched_forget(TgeRtScheduler* s, int64_t request);       // drops a finished request's record
 long long tge_rt_sched_counter(const TgeRtScheduler* s, int which);  // 0 steps 1 tokens 2 preemptions 3 admitted 4 finished
 
+// ---- random weights on the host (random_weights.h: the same values as the device fill kernel) -------
+// Fills out[0..count) with elements first..first+count of the tensor whose key is `key`, as float32
+// (is_bf16 0) or bfloat16 rounded to nearest even (1).  kind 0: normal, value = float(int) * scale;
+// kind 1: uniform, value = float(base + (u32 * span >> 32)) * 2^-24.  Uses up to `threads` threads.
+int tge_rt_random_fill(void* out, int is_bf16, long long count, long long first, unsigned long long key, int kind,
+                       float scale, int base, unsigned int span, int threads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,11 +28,10 @@ from __future__ import annotations
 
 from typing import Dict, Iterator, Tuple
 
-import torch
-
 from ..config.model_spec import LayerSpec, ModelSpec, PartSpec
 from ..config.qwen2 import ARCHITECTURE, Qwen2Config
 from ..registry import Architecture, register_architecture
+from ..weights.draws import Draw, normal, uniform
 
 
 def build_spec(config: Qwen2Config) -> ModelSpec:
@@ -93,22 +92,18 @@ def tensor_shapes(config: Qwen2Config) -> Iterator[Tuple[str, Tuple[int, ...], s
         yield "lm_head.weight", (config.vocab_size, h), "matrix"
 
 
-def random_tensors(config: Qwen2Config, generator: torch.Generator, matrix_dtype: torch.dtype,
-                   device: torch.device) -> Iterator[Tuple[str, torch.Tensor]]:
+def random_plan(config: Qwen2Config) -> Iterator[Tuple[str, Tuple[int, ...], str, Draw]]:
     """Random weights: matrices and biases N(0, 0.02), norm weights 1 + U(-0.1, 0.1).
 
-    Matrices come in ``matrix_dtype``; biases and norm weights in float32.
-    Tensors are yielded one at a time so that a large model never exists twice.
+    (name, shape, role, draw) of every checkpoint tensor; matrices are stored in the run dtype, biases and
+    norm weights in float32.
     """
     for name, shape, kind in tensor_shapes(config):
         if kind == "norm":
-            value = 1.0 + (torch.rand(shape, generator=generator, device=device, dtype=torch.float32) * 0.2 - 0.1)
+            yield name, shape, "vector", uniform(0.9, 1.1)
         else:
-            value = torch.randn(shape, generator=generator, device=device, dtype=torch.float32) * 0.02
-            if kind == "matrix":
-                value = value.to(matrix_dtype)
-        yield name, value
+            yield name, shape, "matrix" if kind == "matrix" else "vector", normal(0.02)
 
 
 register_architecture(Architecture(name=ARCHITECTURE, parse_config=Qwen2Config.from_dict, build_spec=build_spec,
-                                   random_tensors=random_tensors))
+                                   random_plan=random_plan))

@@ -92,6 +92,10 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_apply_penalty", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_sample_cuts", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                           _c_int, _c_int, _c_ptr])
+        _declare(lib, "tge_random_fill", [_c_ptr, _c_int, _c_ll, _c_ll, ctypes.c_ulonglong, _c_int, _c_float, _c_int,
+                                          ctypes.c_uint, _c_ptr])
+        lib.tge_device_sm_count.argtypes = []
+        lib.tge_device_sm_count.restype = _c_int
         lib.tge_sample_cuts_padded.argtypes = [_c_int]
         lib.tge_sample_cuts_padded.restype = _c_ll
         _core_lib = lib
@@ -576,10 +580,10 @@ def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_l
         rows = 64 if max_q_len > 1 else (32 if group <= 32 else 64)
         bq = max(rows // group, 1)
         blocks = (-(-tokens // bq) if max_q_len > 1 else num_seqs) * kv_heads
-    # Two blocks fit on each of the 148 SMs.  All blocks should run at once: a few more than that and the
+    # Two blocks fit on each SM (148 on a B200).  All blocks should run at once: a few more than that and the
     # last ones run alone (batch 16 at context 8,192: 5 splits = 320 blocks took 66 us, 4 splits = 256
     # blocks 52 us; batch 64 at 2,048: 2 splits 56 us, none 47 us).
-    target = 2 * 148
+    target = 2 * core().tge_device_sm_count()
     want_splits = min(target // blocks, -(-max_ctx_len // 128))
     if want_splits <= 1:
         return 0

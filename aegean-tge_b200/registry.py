@@ -10,7 +10,7 @@ everything, and an unknown name is an error that lists the known ones.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Tuple
+from typing import Any, Callable, Dict, Iterable, Tuple
 
 from .config.model_spec import ModelSpec
 from .config.qwen2 import ConfigError
@@ -21,8 +21,9 @@ class Architecture:
     name: str
     parse_config: Callable[[Dict[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
-    # (typed config, generator, dtype name) -> {tensor name: tensor}; see weights/random_init.py
-    random_tensors: Callable[..., Dict[str, Any]]
+    # typed config -> (tensor name, shape, role "matrix" | "vector", weights.draws.Draw) of every checkpoint
+    # tensor: what the random-weights mode draws (weights/random_init.py)
+    random_plan: Callable[[Any], Iterable[Tuple[str, Tuple[int, ...], str, Any]]]
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}

@@ -85,6 +85,8 @@ _SIGNATURES = {
     "tge_rt_sched_tokens": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p]),
     "tge_rt_sched_forget": (c_int, [c_void_p, c_int64]),
     "tge_rt_sched_counter": (c_longlong, [c_void_p, c_int]),
+    "tge_rt_random_fill": (c_int, [c_void_p, c_int, c_longlong, c_longlong, ctypes.c_ulonglong, c_int, ctypes.c_float,
+                                   c_int, ctypes.c_uint, c_int]),
 }
 
 

@@ -4,8 +4,9 @@ tests/golden/tiny_<name>.npz hold logits that the reference's Qwen2 class produc
 (scalar attention and kernels, float32) for the tiny random models A and B: after a whole prompt,
 after single decode steps, for every row of a batch, and for a mixed batch of two sequences
 (tests/golden/make_golden.py made them).  The plain float64 implementation must agree with them to
-float32 rounding.  The weights are regenerated from the seed; if the generator behind them ever
-changes, their hash no longer matches and the comparison is skipped rather than misreported.
+float32 rounding.  The weights are regenerated from the seed by the engine's own counter-based generator,
+whose arithmetic is fixed (csrc/random_weights.h); a hash that no longer matches the golden file's is a
+failure: either the generator or the golden files must be put right (tests/golden/make_golden.py).
 """
 import hashlib
 import os
@@ -26,8 +27,8 @@ def test_plain_matches_the_reference_model(model_dirs, name):
     for key in sorted(weights):
         digest.update(key.encode())
         digest.update(weights[key].float().numpy().astype("<f4").tobytes())
-    if digest.hexdigest() != str(golden["weights_sha256"]):
-        pytest.skip("the seeded weights differ from those the golden files were made with")
+    assert digest.hexdigest() == str(golden["weights_sha256"]), \
+        "the seeded weights differ from those the golden files were made with"
     sequences = {0: [int(t) for t in golden["first"]], 1: [int(t) for t in golden["second"]]}
     full = {s: plain.logits_of(config, weights, tokens).float().numpy() for s, tokens in sequences.items()}
     expected = np.stack([full[int(s)][int(p)] for s, p in zip(golden["row_sequence"], golden["row_position"])])

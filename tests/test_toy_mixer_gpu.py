@@ -18,6 +18,7 @@ def _register():
     from aegean_tge_b200.config.model_spec import LayerSpec, ModelSpec, PartSpec
     from aegean_tge_b200.parts.base import MIXERS, Mixer, ParamSpec, StateSpec
     from aegean_tge_b200.registry import Architecture, register_architecture, registered_architectures
+    from aegean_tge_b200.weights import normal, uniform
 
     if "toy_running_mean" not in MIXERS.names():
         @MIXERS.register("toy_running_mean")
@@ -79,35 +80,35 @@ def _register():
                          PartSpec("token_embedding", sizes, {"weight": "embed"}), norm("final_norm"),
                          PartSpec("linear_head", sizes, {"weight": "head"}))
 
-    def random_tensors(config, generator, matrix_dtype, device):
+    def random_plan(config):
         def mat(*shape):
-            return (torch.randn(shape, generator=generator, device=device) * 0.08).to(matrix_dtype)
+            return tuple(shape), "matrix", normal(0.08)
         def vec(n, around=0.0):
-            return around + torch.randn(n, generator=generator, device=device) * 0.05
-        yield "embed", mat(VOCAB, HIDDEN)
-        yield "head", mat(VOCAB, HIDDEN)
-        yield "final_norm", vec(HIDDEN, 1.0)
+            return (n,), "vector", (uniform(around - 0.08, around + 0.08) if around else normal(0.05))
+        yield ("embed", *mat(VOCAB, HIDDEN))
+        yield ("head", *mat(VOCAB, HIDDEN))
+        yield ("final_norm", *vec(HIDDEN, 1.0))
         for n, kind in enumerate(config["kinds"]):
             p = f"layers.{n}."
-            yield p + "norm1", vec(HIDDEN, 1.0)
-            yield p + "norm2", vec(HIDDEN, 1.0)
+            yield (p + "norm1", *vec(HIDDEN, 1.0))
+            yield (p + "norm2", *vec(HIDDEN, 1.0))
             if kind == "toy":
-                yield p + "mix.weight", mat(HIDDEN, HIDDEN)
+                yield (p + "mix.weight", *mat(HIDDEN, HIDDEN))
             else:
-                yield p + "q.weight", mat(HEADS * HD, HIDDEN)
-                yield p + "k.weight", mat(KV * HD, HIDDEN)
-                yield p + "v.weight", mat(KV * HD, HIDDEN)
-                yield p + "o.weight", mat(HIDDEN, HEADS * HD)
+                yield (p + "q.weight", *mat(HEADS * HD, HIDDEN))
+                yield (p + "k.weight", *mat(KV * HD, HIDDEN))
+                yield (p + "v.weight", *mat(KV * HD, HIDDEN))
+                yield (p + "o.weight", *mat(HIDDEN, HEADS * HD))
                 if kind == "attention_bias":
-                    yield p + "q.bias", vec(HEADS * HD)
-                    yield p + "k.bias", vec(KV * HD)
-                    yield p + "v.bias", vec(KV * HD)
+                    yield (p + "q.bias", *vec(HEADS * HD))
+                    yield (p + "k.bias", *vec(KV * HD))
+                    yield (p + "v.bias", *vec(KV * HD))
             for x, shape in (("gate", (INNER, HIDDEN)), ("up", (INNER, HIDDEN)), ("down", (HIDDEN, INNER))):
-                yield p + f"{x}.weight", mat(*shape)
+                yield (p + f"{x}.weight", *mat(*shape))
 
     if "ToyForTests" not in registered_architectures():
         register_architecture(Architecture("ToyForTests", parse_config=lambda raw: raw, build_spec=build_spec,
-                                           random_tensors=random_tensors))
+                                           random_plan=random_plan))
 
 
 def _plain_logits(config, w, tokens):

@@ -24,6 +24,7 @@ def _register():
     from aegean_tge_b200.parts.base import (FEED_FORWARDS, NORMS, POSITIONS, FeedForward, Norm, ParamSpec,
                                             PositionEncoding)
     from aegean_tge_b200.registry import Architecture, register_architecture, registered_architectures
+    from aegean_tge_b200.weights import normal, uniform
 
     if "toy_routed" not in FEED_FORWARDS.names():
         @FEED_FORWARDS.register("toy_routed")
@@ -131,41 +132,41 @@ def _register():
                          PartSpec("token_embedding", sizes, {"weight": "embed"}), norm("final_norm"),
                          PartSpec("linear_head", sizes, {"weight": "head"}))
 
-    def random_tensors(config, generator, matrix_dtype, device):
+    def random_plan(config):
         def mat(*shape, scale=0.1):
-            return (torch.randn(shape, generator=generator, device=device) * scale).to(matrix_dtype)
+            return tuple(shape), "matrix", normal(scale)
         def vec(n, around=0.0):
-            return around + torch.randn(n, generator=generator, device=device) * 0.05
+            return (n,), "vector", (uniform(around - 0.08, around + 0.08) if around else normal(0.05))
         def norm(name):
-            yield name + ".w", vec(HIDDEN, 1.0)
+            yield (name + ".w", *vec(HIDDEN, 1.0))
             if config["norm"] == "toy_layernorm":
-                yield name + ".b", vec(HIDDEN)
-        yield "embed", mat(VOCAB, HIDDEN)
-        yield "head", mat(VOCAB, HIDDEN)
+                yield (name + ".b", *vec(HIDDEN))
+        yield ("embed", *mat(VOCAB, HIDDEN))
+        yield ("head", *mat(VOCAB, HIDDEN))
         yield from norm("final_norm")
         for n, kind in enumerate(config["ffn"]):
             p = f"layers.{n}."
             yield from norm(p + "norm1")
             yield from norm(p + "norm2")
-            yield p + "q.weight", mat(HEADS * HD, HIDDEN)
-            yield p + "k.weight", mat(KV * HD, HIDDEN)
-            yield p + "v.weight", mat(KV * HD, HIDDEN)
-            yield p + "o.weight", mat(HIDDEN, HEADS * HD)
-            yield p + "q.bias", vec(HEADS * HD)
-            yield p + "k.bias", vec(KV * HD)
-            yield p + "v.bias", vec(KV * HD)
+            yield (p + "q.weight", *mat(HEADS * HD, HIDDEN))
+            yield (p + "k.weight", *mat(KV * HD, HIDDEN))
+            yield (p + "v.weight", *mat(KV * HD, HIDDEN))
+            yield (p + "o.weight", *mat(HIDDEN, HEADS * HD))
+            yield (p + "q.bias", *vec(HEADS * HD))
+            yield (p + "k.bias", *vec(KV * HD))
+            yield (p + "v.bias", *vec(KV * HD))
             if kind == "routed":
                 # a router in float32 with well separated rows, so that bfloat16 rounding of h cannot flip a choice
-                yield p + "router", torch.randn(EXPERTS, HIDDEN, generator=generator, device=device) * 2.0
-                yield p + "w1", mat(EXPERTS, EXPERT_INNER, HIDDEN)
-                yield p + "w2", mat(EXPERTS, HIDDEN, EXPERT_INNER)
+                yield p + "router", (EXPERTS, HIDDEN), "vector", normal(2.0)
+                yield (p + "w1", *mat(EXPERTS, EXPERT_INNER, HIDDEN))
+                yield (p + "w2", *mat(EXPERTS, HIDDEN, EXPERT_INNER))
             else:
                 for x, shape in (("gate", (INNER, HIDDEN)), ("up", (INNER, HIDDEN)), ("down", (HIDDEN, INNER))):
-                    yield p + f"{x}.weight", mat(*shape)
+                    yield (p + f"{x}.weight", *mat(*shape))
 
     if "ToyPartsForTests" not in registered_architectures():
         register_architecture(Architecture("ToyPartsForTests", parse_config=lambda raw: raw, build_spec=build_spec,
-                                           random_tensors=random_tensors))
+                                           random_plan=random_plan))
 
 
 # ---- the same toy architecture on whole sequences, float64, no cache --------------------------------
