@@ -207,7 +207,8 @@ class CacheManager:
         """Creates the page and state tensors (zero-filled, so stale pages hold finite values).
 
         Every group gets one page more than its pool hands out (id ``capacity``): a scratch
-        page that warm-up runs may write without touching a live request.
+        page that warm-up runs may write without touching a live request.  The state tensors likewise
+        have one row more than there are slots (:attr:`scratch_slot`).
         """
         for group in self.groups:
             group.storage = {}
@@ -217,7 +218,7 @@ class CacheManager:
         self.state_storage = {}
         for layer, spec in self.state_specs.items():
             self.state_storage[layer] = {
-                name: torch.zeros((self.max_requests, *shape), dtype=torch.float32, device=device)
+                name: torch.zeros((self.max_requests + 1, *shape), dtype=torch.float32, device=device)
                 for name, shape in spec.entries}
 
     def layer_cache(self, layer: int, source: Optional[int] = None) -> LayerCache:
@@ -291,6 +292,29 @@ class CacheManager:
         for tensors in self.state_storage.values():
             for tensor in tensors.values():
                 tensor[slot].zero_()
+
+    @property
+    def scratch_slot(self) -> int:
+        """A state row that belongs to no request: where warm-up runs and graph captures keep their state."""
+        return self.max_requests
+
+    def snapshot_state(self, slots: Sequence[int]) -> Optional[Tuple[torch.Tensor, List[torch.Tensor]]]:
+        """Copies of the state rows of ``slots`` (None when no layer keeps state), for :meth:`restore_state`."""
+        if not self.state_storage:
+            return None
+        tensors = [t for layer in self.state_storage.values() for t in layer.values()]
+        index = torch.tensor(list(slots), dtype=torch.long, device=tensors[0].device)
+        return index, [t.index_select(0, index) for t in tensors]
+
+    def restore_state(self, snapshot: Optional[Tuple[torch.Tensor, List[torch.Tensor]]]) -> None:
+        """Puts the rows of a snapshot back: a step that ran ahead and is dropped must leave no trace in state
+        that is updated in place (pages need nothing: what it wrote lies beyond the recorded lengths)."""
+        if snapshot is None:
+            return
+        index, rows = snapshot
+        tensors = [t for layer in self.state_storage.values() for t in layer.values()]
+        for tensor, saved in zip(tensors, rows):
+            tensor.index_copy_(0, index, saved)
 
     def pages_missing(self, request: Hashable, total_tokens: int, computed_tokens: Optional[int] = None) -> List[int]:
         """Per group, pages that must be allocated so the request covers ``total_tokens`` positions."""

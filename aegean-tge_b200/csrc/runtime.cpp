@@ -274,29 +274,31 @@ int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int v
     }
   }
   if (reserve) {
-    // everything is reserved before anything runs, so a step either runs whole or not at all
-    std::vector<int64_t> admitted;
-    int rc = 0;
+    // Everything is counted before anything is taken, so a step either runs whole or changes nothing:
+    // state slots for the requests that start here, and per group the pages all portions lack in sum.
+    const int G = (int)cache->groups.size();
+    std::vector<int> lacking(G, 0);
+    int starting = 0;
     for (const PortionView& p : portions) {
-      if (!cache->find(p.request)) {
-        rc = cache->admit(p.request);
-        if (rc < 0) break;
-        admitted.push_back(p.request);
-      }
-      const int total = cache->find(p.request)->computed + p.count;
-      if (total > max_model_len) {
-        rc = fail(TGE_RT_VALUE_ERROR, "request %lld: %d tokens exceed the context of %d", (long long)p.request, total,
-                  max_model_len);
-        break;
-      }
-      rc = cache->grow(p.request, total);
-      if (rc < 0) break;
+      const TgeRtCache::Live* live = cache->find(p.request);
+      const int total = (live ? live->computed : 0) + p.count;
+      if (total > max_model_len)
+        return fail(TGE_RT_VALUE_ERROR, "request %lld: %d tokens exceed the context of %d", (long long)p.request, total,
+                    max_model_len);
+      if (!live) ++starting;
+      for (int g = 0; g < G; ++g) lacking[g] += cache->missing(cache->groups[g], p.request, total);
     }
-    if (rc < 0) {
-      const std::string message = g_error;
-      for (int64_t request : admitted) cache->free_request(request);
-      g_error = message;
-      return rc;
+    if (starting > (int)cache->free_slots.size())
+      return fail(TGE_RT_EXHAUSTED, "cache manager: the step starts %d requests, %d state slots are free", starting,
+                  (int)cache->free_slots.size());
+    for (int g = 0; g < G; ++g)
+      if (lacking[g] > cache->groups[g].pool->free_count())
+        return fail(TGE_RT_EXHAUSTED, "cache manager: the step needs %d more pages of group %d, %d are free", lacking[g], g,
+                    cache->groups[g].pool->free_count());
+    for (const PortionView& p : portions) {
+      if (!cache->find(p.request))
+        if (int rc = cache->admit(p.request); rc < 0) return rc;
+      if (int rc = cache->grow(p.request, cache->find(p.request)->computed + p.count); rc < 0) return rc;
     }
   }
   TgeRtStepLayout L{};

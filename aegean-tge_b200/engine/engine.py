@@ -52,12 +52,14 @@ class Engine:
                  max_tokens: Optional[int] = None, num_pages: Optional[int] = None, max_batch_tokens: int = 2048,
                  max_requests: int = 64, chunk: Optional[int] = None, device: str = "cuda:0",
                  memory_fraction: float = 0.9, random_config: Optional[Dict[str, Any]] = None, seed: int = 0,
-                 page_size: int = PAGE_SIZE, run_ahead: bool = True):
+                 page_size: int = PAGE_SIZE, run_ahead: bool = True, use_graphs: bool = True):
         """``model_dir``: folder with config.json and model.safetensors.  Alternatively
         ``random_config`` (a config.json as a dict) and ``seed``: random weights drawn on the device.
 
         Cache size, first match wins: ``num_pages`` pages per group; ``max_tokens`` cached
         tokens in total; else ``memory_fraction`` of the memory left after the weights.
+        ``run_ahead`` / ``use_graphs``: switches for the step queued ahead and for CUDA graph replay of
+        single-token steps (both on; off for A/B comparisons).
         """
         if not torch.cuda.is_available():
             raise RuntimeError("this engine runs on a CUDA device only; none is available")
@@ -105,7 +107,7 @@ class Engine:
         self.cache.set_pool_sizes(sizes)
         self.cache.allocate_storage(self.dtype, self.device)
         self.model.attach_cache(self.cache)
-        self.runner = ModelRunner(self.model, self.cache, self.max_model_len)
+        self.runner = ModelRunner(self.model, self.cache, self.max_model_len, use_graphs=use_graphs)
         self.scheduler = Scheduler(self.cache, max_batch_tokens=max_batch_tokens, max_requests=max_requests,
                                    max_model_len=self.max_model_len, chunk=chunk,
                                    end_token_ids=self.spec.end_token_ids)
@@ -141,7 +143,8 @@ class Engine:
         does not wait for the host between steps.  The step queued ahead is used only if the scheduler
         then plans exactly that step; otherwise (a request ended on an end token, a new one arrived, pages
         ran out) its results are dropped, the generators it drew from are put back, and the planned step
-        runs as usual.  What it wrote into the cache lies beyond every request's recorded length.
+        runs as usual.  What it wrote into the pages lies beyond every request's recorded length; fixed-size
+        state that mixers update in place is copied before the step ahead runs and put back when it is dropped.
         """
         plan = self.scheduler.schedule()
         ahead, self._ahead = self._ahead, None
@@ -153,6 +156,7 @@ class Engine:
             else:
                 for request, state in zip(ahead["requests"], ahead["rng_states"]):
                     request.rng.state = state
+                self.cache.restore_state(ahead["state"])
                 self.ahead_dropped += 1
         sampling_items = [item for item in plan.items if item.samples]
         if pending is None:
@@ -202,13 +206,14 @@ class Engine:
         for item in plan.items:
             self.cache.set_computed(item.request.id, item.start + item.count)
         states = [r.rng.state for r in requests]
+        snapshot = self.cache.snapshot_state([self.cache.slot_of(name) for name in names])
         try:
             logits = self.runner.step_ahead(names, ids)
         except PoolExhausted:
             return None
         result = self.sampler.sample_async(logits, [r.sampling for r in requests], [r.rng for r in requests])
         return {"requests": requests, "starts": [item.start + 1 for item in plan.items], "rng_states": states,
-                "result": result}
+                "state": snapshot, "result": result}
 
     @staticmethod
     def _matches(ahead, plan) -> bool:

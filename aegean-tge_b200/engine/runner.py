@@ -60,11 +60,17 @@ class Staging:
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, max_model_len: int, use_graphs: bool = True,
-                 max_graph_batch: int = 256):
-        """``use_graphs``: steps made only of single tokens replay a CUDA graph captured per batch size."""
+                 max_graph_batch: int = 256, max_graphs: int = 24):
+        """``use_graphs``: steps made only of single tokens replay a CUDA graph captured per batch size and
+        context bound.  At most ``max_graphs`` are kept (the one used longest ago goes first); all of them
+        allocate from one memory pool, which is safe because replays never overlap: they run one after the
+        other on the step's stream."""
         self.use_graphs = use_graphs and model.graph_safe      # a part that works from host values runs eagerly
         self.max_graph_batch = max_graph_batch
-        self._graphs: Dict[tuple, "DecodeGraph"] = {}
+        self.max_graphs = max_graphs
+        self._graphs: Dict[tuple, "DecodeGraph"] = {}          # in order of last use
+        self._graph_pool = None
+        self.graphs_captured = 0
         self.graph_replays = 0
         self.model = model
         self.cache = cache
@@ -173,9 +179,15 @@ class ModelRunner:
             while bound < max_ctx:
                 bound *= 2
             bound = min(bound, self.max_model_len)
-            graph = self._graphs.get((batch, bound))
+            graph = self._graphs.pop((batch, bound), None)
             if graph is None:
-                graph = self._graphs[(batch, bound)] = DecodeGraph(self, batch, bound)
+                while len(self._graphs) >= self.max_graphs:
+                    del self._graphs[next(iter(self._graphs))]
+                if self._graph_pool is None:
+                    self._graph_pool = torch.cuda.graph_pool_handle()
+                graph = DecodeGraph(self, batch, bound)
+                self.graphs_captured += 1
+            self._graphs[(batch, bound)] = graph
             logits = graph.run(pack, packed, device_tokens)
             self.ops.launches += graph.kernels
             self.h2d_bytes_last = graph.nbytes
@@ -236,8 +248,9 @@ class DecodeGraph:
         L.max_q_len, L.max_ctx_len, L.total_ints = 1, max_ctx, cursor
         self.staging = Staging(cursor)
         self.dev = torch.zeros(cursor, dtype=torch.int32, device=device)
-        # warm-up contents: every request one token at position 0 on the scratch page
+        # warm-up contents: every request one token at position 0 on the scratch page, its state in the scratch slot
         warm = self.staging.views[0]
+        warm[L.slots:L.slots + batch] = cache.scratch_slot
         warm[L.seq_of_token:L.seq_of_token + batch] = np.arange(batch)
         warm[L.q_start:L.q_start + batch + 1] = np.arange(batch + 1)
         warm[L.logit_rows:L.logit_rows + batch] = np.arange(batch)
@@ -259,7 +272,7 @@ class DecodeGraph:
         torch.cuda.synchronize(device)
         before = ops.launches
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, pool=runner._graph_pool):
             self.logits = model.forward(self.ctx, self.rows)
         self.kernels = ops.launches - before
         ops.launches = before

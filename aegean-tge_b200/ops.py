@@ -183,6 +183,7 @@ _FLOAT = (torch.float32, torch.bfloat16)
 # ----------------------------------------------------------------------------
 _status: Dict[int, torch.Tensor] = {}
 _scratch: Dict[int, torch.Tensor] = {}
+_outgrown: Dict[int, list] = {}       # earlier scratch buffers, kept alive for the graphs that hold their address
 
 
 def status_word(device: Optional[torch.device] = None) -> torch.Tensor:
@@ -203,7 +204,13 @@ def check_status() -> None:
 
 
 def scratch_floats(count: int) -> torch.Tensor:
-    """A float32 scratch buffer of at least ``count`` elements, reused between calls."""
+    """A float32 scratch buffer of at least ``count`` elements, reused between calls.
+
+    The buffer grows when a call needs more (never while a CUDA graph is being captured).  A buffer that
+    was outgrown is kept, not freed: a graph captured earlier has its address in its kernels and goes on
+    writing partial sums there whenever it is replayed.  Buffers at least double, so what is kept is less
+    than what is in use.
+    """
     index = torch.cuda.current_device()
     have = _scratch.get(index)
     if have is None or have.numel() < count:
@@ -211,6 +218,8 @@ def scratch_floats(count: int) -> torch.Tensor:
             raise KernelError("scratch memory must be sized before a CUDA graph is captured "
                               f"(need {count} floats, have {0 if have is None else have.numel()})")
         size = max(count, 1 << 22, 0 if have is None else 2 * have.numel())
+        if have is not None:
+            _outgrown.setdefault(index, []).append(have)
         _scratch[index] = torch.empty(size, dtype=torch.float32, device=f"cuda:{index}")
     return _scratch[index]
 

@@ -177,3 +177,44 @@ def test_random_orders_lose_no_page(seed):
         m.free(name)
     m.check()
     assert all(g.pool.free_count == g.pool.capacity for g in m.groups) and m.free_slots == 5
+
+
+def test_a_step_that_does_not_fit_takes_nothing():
+    """The packer reserves a whole step or nothing: when the portions' pages do not fit in sum, requests that
+    were live keep exactly what they had and requests that would have started are not admitted."""
+    import ctypes
+
+    import numpy as np
+
+    from aegean_tge_b200 import runtime as rt
+    from aegean_tge_b200.engine.batch import Portion, PortionArrays
+    m = _manager(pages=6, slots=3, specs=(FULL, WINDOW))
+    lib = rt.lib()
+
+    def pack(portions):
+        arrays = PortionArrays(m, portions)
+        out = np.zeros(4096, dtype=np.int32)
+        layout = rt.StepLayout()
+        try:
+            return rt.check(lib.tge_rt_step_pack(m.native, arrays.count, arrays.handles, arrays.token_ptrs,
+                                                 arrays.token_counts, arrays.want_ptrs, arrays.want_counts, 100, 512, 0, 0,
+                                                 out.ctypes.data, out.size, ctypes.byref(layout)))
+        finally:
+            m.forget_dead_handles()
+
+    pack([Portion("a", [1] * 20, []), Portion("b", [2] * 10, [])])           # a: 2 pages, b: 1 page per group
+    lib.tge_rt_cache_advance(m.native, (ctypes.c_int64 * 2)(m.handle_of("a"), m.handle_of("b")), (ctypes.c_int * 2)(20, 10), 2)
+    before = [(g.pool.free_count, g.tables["a"], g.tables["b"]) for g in m.groups]
+    # a grows by one page and b by one: fine alone, but c's three pages make it five where three are free
+    with pytest.raises(PoolExhausted):
+        pack([Portion("a", [1] * 20, []), Portion("b", [2] * 10, []), Portion("c", [3] * 40, [])])
+    assert [(g.pool.free_count, g.tables["a"], g.tables["b"]) for g in m.groups] == before
+    assert not m.is_live("c") and m.free_slots == 1
+    m.check()
+    # more new requests than slots: nothing is admitted either
+    with pytest.raises(PoolExhausted):
+        pack([Portion("c", [3], []), Portion("d", [4], [])])
+    assert not m.is_live("c") and not m.is_live("d") and m.free_slots == 1
+    assert [(g.pool.free_count, g.tables["a"], g.tables["b"]) for g in m.groups] == before
+    pack([Portion("a", [1] * 20, []), Portion("b", [2] * 10, [])])           # the smaller step still runs
+    m.check()

@@ -214,3 +214,34 @@ def test_many_decode_rows(shape, dtype):
     want = torch.stack([ref[r % 5][prompt[r] + 1] for r in some])
     _close(second, want, dtype, f"{shape} 64 decode rows")
     ops.check_status()
+
+
+def test_a_captured_graph_survives_the_growth_of_the_scratch_buffer():
+    """The products' partial sums go to one scratch buffer whose address a captured decode graph holds.  A later
+    prompt portion that needs a larger buffer must leave the old one alive: the graph is replayed afterwards
+    and must still give what an engine without graphs gives."""
+    from aegean_tge_b200 import ops
+    device = torch.cuda.current_device()
+    if device in ops._scratch:                       # start from the smallest buffer, as a fresh process would
+        ops._outgrown.setdefault(device, []).append(ops._scratch.pop(device))
+    tokens = _tokens("7B", 40, salt=9)
+    long_prompt = _tokens("7B", 512, salt=10)
+    outputs = []
+    for use_graphs in (True, False):
+        engine = _engine("7B", "bfloat16", use_graphs=use_graphs, run_ahead=False, max_tokens=4096)
+        rows = [_pick(engine.runner.step([_portion("r", tokens[:8])]))]
+        for t in range(8, 24):
+            rows.append(_pick(engine.runner.step([_portion("r", tokens[t:t + 1])])))
+        small = ops._scratch[device].numel()
+        engine.runner.step([_portion("big", long_prompt, [])])
+        if use_graphs:
+            assert ops._scratch[device].numel() > small, "the long portion was meant to outgrow the scratch buffer"
+            assert any(old.numel() == small for old in ops._outgrown[device])
+        for t in range(24, 40):
+            rows.append(_pick(engine.runner.step([_portion("r", tokens[t:t + 1])])))
+        assert engine.runner.graph_replays == (32 if use_graphs else 0)
+        outputs.append(torch.cat(rows))
+        del engine
+    ops.check_status()
+    assert torch.equal(outputs[0], outputs[1])
+    _close(outputs[0], _oracle("7B").logits("bfloat16", tokens), "bfloat16", "7B decode around a scratch growth")

@@ -52,9 +52,25 @@ def _register():
                     begin += count
                 return out
 
-    def names(n):
-        p = f"layers.{n}."
-        return p
+    if "toy_running_mean_on_device" not in MIXERS.names():
+        @MIXERS.register("toy_running_mean_on_device")
+        class RunningMeanOnDevice(MIXERS.get("toy_running_mean")):
+            """The same mixer working from the step's device arrays only (``ctx.slots``, ``ctx.q_start``): no host
+            lists, no synchronisation, so single-token steps may be replayed from a CUDA graph and queued ahead."""
+            graph_safe = True
+
+            def forward(self, h, ctx, cache):
+                seq, slots = ctx.seq_of_token.long(), ctx.slots.long()
+                part = h.float()
+                summed = torch.cumsum(part, dim=0)
+                first = ctx.q_start[:-1].long()
+                before = summed[first] - part[first]                      # the sum of everything before each portion
+                running = cache.state["sum"][slots][seq] + (summed - before[seq])
+                seen = (ctx.positions + 1).float()[:, None]                # tokens of the request up to and with this one
+                last = ctx.q_start[1:].long() - 1
+                cache.state["sum"].index_copy_(0, slots, running[last])
+                cache.state["count"].index_copy_(0, slots, seen[last])
+                return ((running / seen) @ self.weight.float().T).to(h.dtype)
 
     def build_spec(config):
         position = PartSpec("rope_neox", {"head_dim": HD, "theta": 777.0})
@@ -62,8 +78,9 @@ def _register():
         layers = []
         for n, kind in enumerate(config["kinds"]):
             p = f"layers.{n}."
-            if kind == "toy":
-                mixer = PartSpec("toy_running_mean", {"hidden_size": HIDDEN}, {"mix.weight": p + "mix.weight"})
+            if kind in ("toy", "toy_on_device"):
+                mixer = PartSpec("toy_running_mean" if kind == "toy" else "toy_running_mean_on_device",
+                                 {"hidden_size": HIDDEN}, {"mix.weight": p + "mix.weight"})
             else:
                 mixer = PartSpec("gqa_attention",
                                  {"hidden_size": HIDDEN, "heads": HEADS, "kv_heads": KV, "head_dim": HD,
@@ -78,7 +95,8 @@ def _register():
         sizes = {"vocab_size": VOCAB, "hidden_size": HIDDEN}
         return ModelSpec("ToyForTests", HIDDEN, VOCAB, 256, tuple(layers), tuple(config["schedule"]),
                          PartSpec("token_embedding", sizes, {"weight": "embed"}), norm("final_norm"),
-                         PartSpec("linear_head", sizes, {"weight": "head"}))
+                         PartSpec("linear_head", sizes, {"weight": "head"}),
+                         end_token_ids=tuple(config.get("end_token_ids", ())))
 
     def random_plan(config):
         def mat(*shape):
@@ -92,7 +110,7 @@ def _register():
             p = f"layers.{n}."
             yield (p + "norm1", *vec(HIDDEN, 1.0))
             yield (p + "norm2", *vec(HIDDEN, 1.0))
-            if kind == "toy":
+            if kind in ("toy", "toy_on_device"):
                 yield (p + "mix.weight", *mat(HIDDEN, HIDDEN))
             else:
                 yield (p + "q.weight", *mat(HEADS * HD, HIDDEN))
@@ -121,7 +139,7 @@ def _plain_logits(config, w, tokens):
         kind = config["kinds"][n]
         p = f"layers.{n}."
         h = plain.rms_norm(x, w[p + "norm1"], 1e-5)
-        if kind == "toy":
+        if kind in ("toy", "toy_on_device"):
             mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=h.dtype)[:, None]
             x = x + mean @ w[p + "mix.weight"].T
         else:
@@ -157,7 +175,7 @@ def _engine_and_weights(config, dtype):
         p = f"layers.{n}."
         w[p + "norm1"] = block.mixer_norm.weight.double().cpu()
         w[p + "norm2"] = block.ffn_norm.weight.double().cpu()
-        if config["kinds"][n] == "toy":
+        if config["kinds"][n] in ("toy", "toy_on_device"):
             w[p + "mix.weight"] = block.mixer.weight.double().cpu()
         else:
             qkv = block.mixer.w_qkv.double().cpu()
@@ -221,3 +239,51 @@ def test_a_layer_may_run_twice():
     logits = engine.runner.step([Portion("r", tokens, list(range(len(tokens))))])
     assert logits.shape == (len(tokens), VOCAB) and torch.isfinite(logits).all()
     assert engine.model.step_param_bytes() > 0
+
+
+def _generate_with_arrivals(config, end_tokens, **engine_kw):
+    """Three requests drawn at temperature 1 (the sampler stays on the device); the second and third arrive
+    while the first is decoding.  Returns ({request: tokens}, engine)."""
+    from aegean_tge_b200 import Engine, SamplingParams
+    _register()
+    raw = dict(config, architectures=["ToyForTests"], end_token_ids=list(end_tokens))
+    engine = Engine(random_config=raw, seed=3, dtype="float32", context=256, max_tokens=1024, max_requests=4, **engine_kw)
+    rnd = random.Random(11)
+    prompts = {name: [rnd.randrange(VOCAB) for _ in range(n)] for name, n in (("a", 9), ("b", 21), ("c", 5))}
+    sampling = lambda seed: SamplingParams(temperature=1.0, seed=seed)
+    engine.add_request(prompts["a"], n=40, sampling=sampling(1), request_id="a")
+    outputs, steps = {}, 0
+    while engine.has_unfinished():
+        for request in engine.step():
+            outputs[request.id] = list(request.output)
+        steps += 1
+        if steps == 6:          # "a" decodes alone from slot 0 (its batch-1 graph exists) when "b" arrives
+            engine.add_request(prompts["b"], n=30, sampling=sampling(2), request_id="b")
+        if steps == 15:
+            engine.add_request(prompts["c"], n=12, sampling=sampling(3), request_id="c")
+    return outputs, engine
+
+
+def test_state_is_safe_under_steps_queued_ahead_and_graph_capture():
+    """A graph-safe mixer that updates its state slot in place.  A step queued ahead and then dropped (a request
+    ended on an end token, a request arrived) must not have advanced the state, and capturing a decode graph
+    for a new batch size while a request lives in slot 0 must not touch slot 0: the tokens are those of an
+    engine that neither queues ahead nor replays graphs, and the last logits agree with the plain model."""
+    config = {"kinds": ["toy_on_device", "attention_bias", "toy_on_device"], "schedule": [0, 1, 2]}
+    free_run, _ = _generate_with_arrivals(config, (), run_ahead=False, use_graphs=False)
+    # an end token that cuts at least one request short, but none before its fourth token
+    end = None
+    for token in range(VOCAB):
+        firsts = [out.index(token) for out in free_run.values() if token in out]
+        if firsts and min(firsts) >= 3 and any(token in out[:-3] for out in free_run.values()):
+            end = token
+            break
+    assert end is not None
+    plain_run, plain_engine = _generate_with_arrivals(config, (end,), run_ahead=False, use_graphs=False)
+    fast_run, fast_engine = _generate_with_arrivals(config, (end,))
+    assert any(out[-1] == end and len(out) < n for out, n in ((plain_run["a"], 40), (plain_run["b"], 30), (plain_run["c"], 12)))
+    assert fast_run == plain_run
+    stats = fast_engine.stats()["steps_queued_ahead"]
+    assert stats["used"] > 0 and stats["dropped"] > 0, stats
+    assert fast_engine.runner.graphs_captured >= 2 and fast_engine.runner.graph_replays > 0
+    assert plain_engine.runner.graph_replays == 0 and plain_engine.stats()["steps_queued_ahead"]["used"] == 0
