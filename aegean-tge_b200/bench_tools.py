@@ -23,22 +23,9 @@ def _random_tokens(vocab: int, count: int, seed: int) -> List[int]:
 
 
 def prefill_flops(engine, tokens: int) -> float:
-    """Multiply-adds of one whole prompt, times two: the products plus causal attention."""
-    model = engine.model
-    matrix_params = 0
-    attention = 0.0
-    for index in engine.spec.schedule:
-        block = model.blocks[index]
-        for part in block.parts().values():
-            for name in ("w_qkv", "w_o", "w_gate_up", "w_down"):
-                w = getattr(part, name, None)
-                if w is not None:
-                    matrix_params += w.numel()
-        mixer = block.mixer
-        if hasattr(mixer, "heads"):
-            attention += 4.0 * mixer.heads * mixer.head_dim * tokens * (tokens + 1) / 2.0
-    head = model.head.weight.numel()          # one row of logits
-    return 2.0 * tokens * matrix_params + attention + 2.0 * head
+    """Operations of one whole prompt (a multiply-add is two): what the model's parts report for ``tokens``
+    tokens under a causal mask, and one row of logits."""
+    return engine.model.step_flops(tokens, tokens * (tokens + 1) / 2.0, 1)
 
 
 def bench_prefill(engine, prompt_len: int, repeat: int = 3, warmup: int = 2) -> Dict[str, float]:

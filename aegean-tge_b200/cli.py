@@ -155,20 +155,25 @@ def command_info(args) -> int:
 
 
 def command_plan(args) -> int:
-    """Bytes before loading, in the manner of the reference's planner (src/models/plan.cpp:28-133)."""
-    from .config.qwen2 import read_config_json
-    from .registry import architecture_of
+    """Bytes before loading, in the manner of the reference's planner (src/models/plan.cpp:28-133).  The model
+    is put together on paper (its parts, no weights, no GPU) and asked what it holds and what a step reads."""
+    import torch
+    from .config.common import read_config_json
+    from .engine.engine import PAGE_SIZE
+    from .models.decoder import DecoderModel
+    from .parts.base import BuildEnv
     from .peaks import hbm_gbs
+    from .registry import architecture_of
+    from .weights.random_init import parse_dtype
     raw = read_config_json(args.model)
     arch = architecture_of(raw)
-    config = arch.parse_config(raw)
-    element = 2 if args.dtype == "bfloat16" else 4
-    h, q, kv, ff, v = config.hidden_size, config.q_dim, config.kv_dim, config.intermediate_size, config.vocab_size
-    per_layer = (q + 2 * kv) * h + h * q + 3 * ff * h
-    matrices = config.num_hidden_layers * per_layer + v * h
-    weights = (matrices + (0 if config.tie_word_embeddings else v * h)) * element
-    decode_bytes = matrices * element                       # everything but the embedding rows (plan.cpp:42-46)
-    kv_per_token = config.num_hidden_layers * 2 * kv * element
+    spec = arch.build_spec(arch.parse_config(raw))
+    env = BuildEnv(dtype=parse_dtype(args.dtype), device=torch.device("cpu"), hidden_size=spec.hidden_size,
+                   max_positions=min(spec.max_positions, args.context), page_size=PAGE_SIZE, ops=None)
+    model = DecoderModel(spec, env)
+    weights = model.weight_bytes()
+    decode_bytes = model.step_param_bytes()                 # everything but the embedding rows (plan.cpp:42-46)
+    kv_per_token = model.cache_bytes_per_token()
     bandwidth = args.bandwidth or hbm_gbs()
     total = weights + args.sessions * args.context * kv_per_token
     print(f"weights  : {weights / 2**30:.2f} GiB ({args.dtype})")
@@ -223,10 +228,8 @@ def command_generate(args) -> int:
     for token in prompt:
         if not 0 <= token < engine.spec.vocab_size:
             raise UsageError(f"generate: token {token} is outside the vocabulary")
-    config = engine.config
-    print(f"model    : {args.model or args.random_config}, {facts['layers']} layers, {facts['hidden_size']} dim, "
-          f"{getattr(config, 'num_attention_heads', '?')}/{getattr(config, 'num_key_value_heads', '?')} heads, "
-          f"vocab {facts['vocab_size']}")
+    print(f"model    : {args.model or args.random_config}, {facts['layers']} layers ({facts['layer_kinds']}), "
+          f"{facts['hidden_size']} dim, vocab {facts['vocab_size']}")
     if not engine.spec.end_token_ids:
         print("generate: warning: model declares no end-of-generation ids; stopping only at --n", file=sys.stderr)
     request_id = engine.add_request(prompt, args.n, sampling)

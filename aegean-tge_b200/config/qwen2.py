@@ -32,11 +32,9 @@ import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, Tuple
 
+from .common import ConfigError, read_config_json  # noqa: F401  (ConfigError is raised below)
+
 ARCHITECTURE = "Qwen2ForCausalLM"
-
-
-class ConfigError(ValueError):
-    """A config.json that cannot describe a model this engine runs."""
 
 
 def _need_int(raw: Dict[str, Any], key: str, *, minimum: int = 1) -> int:
@@ -197,17 +195,3 @@ class Qwen2Config:
             out["eos_token_id"] = (self.end_token_ids[0] if len(self.end_token_ids) == 1
                                    else list(self.end_token_ids))
         return out
-
-
-def read_config_json(model_dir: str) -> Dict[str, Any]:
-    path = os.path.join(model_dir, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"{model_dir}: no config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as handle:
-            raw = json.load(handle)
-    except json.JSONDecodeError as error:
-        raise ConfigError(f"{path}: not valid JSON ({error})") from error
-    if not isinstance(raw, dict):
-        raise ConfigError(f"{path}: top level must be an object")
-    return raw

@@ -90,15 +90,17 @@ __device__ __forceinline__ unsigned long long global_timer() {
   return t;
 }
 
-// Bounded wait.  Returns false when it gave up or when another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag) {
+// Bounded wait.  Returns false when it gave up (after `limit_ns` nanoseconds) or when another role already did.
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long start = global_timer();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 1023u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer() - start > 2000000000ull) {
+      if (global_timer() - start > limit_ns) {
         *abort_flag = 1;
         atomicOr(status, TGE_STATUS_WAIT_TIMEOUT);
         return false;
@@ -856,6 +858,31 @@ bool choose_pair(int M, int N, int K, long long scratch_floats, const Plan& sing
 
 // 0: never pair two SMs on a tile; 1: where it is expected to be faster (the default); 2: wherever possible.
 TGE_API void tge_gemm_tcgen05_pair_mode(int mode) { g_pair_mode = mode; }
+
+// One thread waits, through the product kernels' own bounded wait, on a barrier at which nothing ever arrives:
+// the wait must give up after `limit_ns`, set the status bit and let the kernel return.  outcome[0] = 1 if the
+// wait reported success (it must not), outcome[1] = the nanoseconds it took.
+__global__ void wait_gives_up_kernel(int* status, unsigned long long limit_ns, long long* outcome) {
+  __shared__ __align__(8) unsigned long long barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&barrier), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    const unsigned long long start = global_timer();
+    const bool arrived = mbar_wait(smem_u32(&barrier), 0, status, &abort_flag, limit_ns);
+    outcome[0] = arrived ? 1 : 0;
+    outcome[1] = (long long)(global_timer() - start);
+  }
+}
+
+// For tests of the status word: limits above 10 ms are refused, so nothing launched here can wait for long.
+TGE_API int tge_wait_gives_up(int* status, long long limit_ns, long long* outcome, cudaStream_t stream) {
+  TGE_REQUIRE(status != nullptr && outcome != nullptr, "wait_gives_up: null pointer");
+  TGE_REQUIRE(limit_ns > 0 && limit_ns <= 10000000ll, "wait_gives_up: the limit must lie in (0, 10 ms], got %lld ns", limit_ns);
+  wait_gives_up_kernel<<<1, 32, 0, stream>>>(status, (unsigned long long)limit_ns, outcome);
+  return tge_launched("wait_gives_up", 1);
+}
 // What the product of these sizes would run as: out = {two SMs per tile?, token tile, stages, k-splits}.
 TGE_API void tge_gemm_tcgen05_describe(int M, int N, int K, int* out) {
   const Plan plan = make_plan(M, N, K, (long long)1 << 60, 0, 0);

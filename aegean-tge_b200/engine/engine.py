@@ -27,7 +27,7 @@ import torch
 from .. import ops as _ops
 from .. import runtime as _rt
 from ..cache.manager import CacheManager
-from ..config.qwen2 import ConfigError, read_config_json
+from ..config.common import ConfigError, read_config_json
 from ..models.decoder import DecoderModel
 from ..parts.base import BuildEnv
 from ..registry import architecture_of
@@ -259,7 +259,12 @@ class Engine:
         return out
 
     def describe(self) -> Dict[str, Any]:
+        kinds: Dict[str, int] = {}
+        for layer in self.spec.layers:
+            name = f"{layer.mixer.kind}+{layer.feed_forward.kind}"
+            kinds[name] = kinds.get(name, 0) + 1
         return {
+            "layer_kinds": ", ".join(f"{count} x {name}" for name, count in kinds.items()),
             "architecture": self.spec.architecture, "dtype": str(self.dtype).replace("torch.", ""),
             "layers": len(self.spec.layers), "hidden_size": self.spec.hidden_size, "vocab_size": self.spec.vocab_size,
             "max_model_len": self.max_model_len, "page_size": self.cache.page_size,

@@ -98,10 +98,34 @@ class DecoderModel:
                              for index, layer in enumerate(self.spec.layers)]
 
     def cache_bytes_per_token(self) -> int:
+        """Bytes of paged cache one token adds, over all layers that keep one (their ``cache_spec``)."""
         total = 0
         for block, layer in zip(self.blocks, self.spec.layers):
-            if layer.cache_from is None and hasattr(block.mixer, "cache_bytes_per_token"):
-                total += block.mixer.cache_bytes_per_token()
+            spec = block.mixer.cache_spec() if layer.cache_from is None else None
+            if spec is not None:
+                for _name, shape in spec.entries:
+                    count = 1
+                    for extent in shape:
+                        count *= int(extent)
+                    total += count * self.env.dtype.itemsize
+        return total
+
+    def weight_bytes(self) -> int:
+        """Bytes of all parameters on the device, a tensor that two parts share counted once."""
+        total = 0
+        for param, _where in self.manifest().values():
+            count = 1
+            for extent in param.shape:
+                count *= int(extent)
+            total += count * (self.env.dtype.itemsize if param.role == "matrix" else 4)
+        return total
+
+    def step_flops(self, tokens: int, pairs: float, rows: int) -> float:
+        """Floating-point operations of one step: ``tokens`` tokens through every scheduled layer, their queries
+        meeting ``pairs`` (query, key) pairs per layer, and ``rows`` rows of logits."""
+        total = self.head.flops(rows, 0.0)
+        for index in self.spec.schedule:
+            total += sum(part.flops(tokens, pairs) for part in self.blocks[index].parts().values())
         return total
 
     # -- one step -------------------------------------------------------------

@@ -94,6 +94,7 @@ def core() -> ctypes.CDLL:
                                           _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_random_fill", [_c_ptr, _c_int, _c_ll, _c_ll, ctypes.c_ulonglong, _c_int, _c_float, _c_int,
                                           ctypes.c_uint, _c_ptr])
+        _declare(lib, "tge_wait_gives_up", [_c_ptr, _c_ll, _c_ptr, _c_ptr])
         lib.tge_device_sm_count.argtypes = []
         lib.tge_device_sm_count.restype = _c_int
         lib.tge_sample_cuts_padded.argtypes = [_c_int]
@@ -201,6 +202,17 @@ def check_status() -> None:
         word.zero_()
         what = [text for bit, text in STATUS_BITS.items() if value & bit]
         raise DeviceStatusError("a kernel met " + " and ".join(what or [f"status {value}"]))
+
+
+def wait_gives_up(limit_ns: int = 1_000_000) -> Tuple[bool, int]:
+    """Launches one thread that waits, with the product kernels' bounded wait and a limit of ``limit_ns``
+    (at most 10 ms), on a barrier nothing arrives at.  Returns (whether the wait claimed success, nanoseconds
+    it took); the status word then carries the time-out bit until :func:`check_status` reads it."""
+    lib = core()
+    outcome = torch.zeros(2, dtype=torch.int64, device=f"cuda:{torch.cuda.current_device()}")
+    _check(lib.tge_wait_gives_up(status_word().data_ptr(), int(limit_ns), outcome.data_ptr(), _stream()), lib)
+    arrived, took = outcome.tolist()
+    return bool(arrived), int(took)
 
 
 def scratch_floats(count: int) -> torch.Tensor:

@@ -79,20 +79,14 @@ class GQAttention(Mixer):
         self.w_o = tensors["o.weight"].contiguous()
         self.b_o = tensors["o.bias"].contiguous() if self.o_bias else None
 
-    def param_bytes(self) -> int:
-        total = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
-        for b in (self.b_qkv, self.b_o):
-            if b is not None:
-                total += b.numel() * 4
-        return total
+    def flops(self, tokens: int, pairs: float) -> float:
+        products = 2.0 * tokens * (self.q_dim + 2 * self.kv_dim + self.q_dim) * self.hidden
+        return products + 4.0 * self.heads * self.head_dim * pairs         # scores and weighted values
 
     def cache_spec(self) -> Optional[PagedCacheSpec]:
         entry = (self.kv_heads, self.head_dim)
         return PagedCacheSpec(entries=(("k", entry), ("v", entry)),
                               window=None if self.window is None else int(self.window))
-
-    def cache_bytes_per_token(self) -> int:
-        return 2 * self.kv_dim * (2 if self.env.dtype == torch.bfloat16 else 4)
 
     def attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         """Everything up to, not including, the output projection: [T, heads*head_dim]."""

@@ -150,9 +150,23 @@ class Part:
         if tensors:
             raise ValueError(f"{type(self).__name__} takes no parameters")
 
-    # bytes this part reads from its parameters in one step (for the roofline)
     def param_bytes(self) -> int:
-        return 0
+        """Bytes this part reads from its parameters in one step (for the roofline and the planner): every
+        declared parameter once, matrices in the run dtype, vectors in float32, tables in int32.  It needs
+        no loaded weights."""
+        total = 0
+        for param in self.param_specs().values():
+            count = 1
+            for extent in param.shape:
+                count *= int(extent)
+            total += count * (self.env.dtype.itemsize if param.role == "matrix" else 4)
+        return total
+
+    def flops(self, tokens: int, pairs: float) -> float:
+        """Floating-point operations of one step of ``tokens`` tokens whose queries meet ``pairs`` (query, key)
+        pairs in all (a whole prompt of T tokens: T (T + 1) / 2), a multiply-add counted as two.  Parts that
+        only move or scale data report 0."""
+        return 0.0
 
 
 class Norm(Part):

@@ -31,6 +31,9 @@ class TokenEmbedding(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
+    def param_bytes(self) -> int:
+        return 0        # a step reads the rows of its tokens, not the table
+
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return self.ops.embedding(self.weight, token_ids)
 
@@ -52,8 +55,8 @@ class LinearHead(Part):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
-    def param_bytes(self) -> int:
-        return self.weight.numel() * self.weight.element_size()
+    def flops(self, tokens: int, pairs: float) -> float:
+        return 2.0 * tokens * self.vocab * self.hidden
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return self.ops.linear(h, self.weight, None, self.ops.GEMM_STORE_F32)

@@ -43,8 +43,8 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * self.inner, self.hidden).contiguous()
         self.w_down = tensors["down.weight"].contiguous()
 
-    def param_bytes(self) -> int:
-        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+    def flops(self, tokens: int, pairs: float) -> float:
+        return 2.0 * tokens * 3 * self.inner * self.hidden
 
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)

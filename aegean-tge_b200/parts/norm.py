@@ -33,9 +33,6 @@ class RMSNorm(Norm):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
 
-    def param_bytes(self) -> int:
-        return self.size * 4
-
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return self.ops.rmsnorm(x, self.weight, self.eps, self.env.dtype, rows=rows)
 

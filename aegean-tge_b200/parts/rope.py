@@ -32,6 +32,9 @@ def rotary_tables(theta: float, rotary: int, positions: int) -> Tuple[torch.Tens
     return torch.cos(angle.double()).float(), torch.sin(angle.double()).float()
 
 
+_TABLES: dict = {}
+
+
 @POSITIONS.register("rope_neox")
 class RotaryNeoX(PositionEncoding):
     """params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default head_dim)."""
@@ -46,9 +49,14 @@ class RotaryNeoX(PositionEncoding):
             raise ValueError(f"rope: rotary width {self.rotary} must be even and within head_dim {self.head_dim}")
         if not self.theta > 0:
             raise ValueError("rope: theta must be positive")
-        cos, sin = rotary_tables(self.theta, self.rotary, env.max_positions)
-        self.cos = cos.to(env.device).contiguous()
-        self.sin = sin.to(env.device).contiguous()
+        # layers with the same base, width and length share one pair of tables
+        key = (self.theta, self.rotary, env.max_positions, str(env.device))
+        if key not in _TABLES:
+            if len(_TABLES) >= 8:
+                _TABLES.pop(next(iter(_TABLES)))
+            cos, sin = rotary_tables(self.theta, self.rotary, env.max_positions)
+            _TABLES[key] = (cos.to(env.device).contiguous(), sin.to(env.device).contiguous())
+        self.cos, self.sin = _TABLES[key]
 
     def rotary_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor, int]]:
         return self.cos, self.sin, self.rotary

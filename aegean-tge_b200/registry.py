@@ -13,7 +13,7 @@ from dataclasses import dataclass
 from typing import Any, Callable, Dict, Iterable, Tuple
 
 from .config.model_spec import ModelSpec
-from .config.qwen2 import ConfigError
+from .config.common import ConfigError
 
 
 @dataclass(frozen=True)

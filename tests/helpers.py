@@ -17,8 +17,19 @@ def rel_error(got: torch.Tensor, ref: torch.Tensor) -> float:
 # Tolerances, fixed once: float32 kernels differ from float64 by summation rounding;
 # bfloat16 results carry one rounding of the output (2^-9) plus rounded intermediates.
 TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
-# Whole-model logits: rounding accumulates over layers.
-MODEL_TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+# Whole-model logits against the float64 plain model with float32 weights, relative to the largest logit:
+# about three times the largest error seen on a B200 (float32 2.4e-6 with the toy parts, 9e-7 otherwise;
+# bfloat16 1.1e-2 with the toy parts).  Per tiny configuration the bfloat16 bound is tighter: model_tol().
+MODEL_TOL = {"float32": 1e-5, "bfloat16": 3.5e-2}
+# largest bfloat16 error seen: A 3.1e-3, B 7.8e-3, C 7.0e-3, D 8.8e-3, E 4.1e-3
+_BFLOAT16_TOL = {"A": 1e-2, "B": 2.5e-2, "C": 2.2e-2, "D": 2.7e-2, "E": 1.3e-2}
+
+
+def model_tol(dtype: str, name: str = "") -> float:
+    """The bound for whole-model logits of tiny configuration ``name`` (the general bound if it has none)."""
+    if dtype == "bfloat16":
+        return _BFLOAT16_TOL.get(name, MODEL_TOL[dtype])
+    return MODEL_TOL[dtype]
 
 
 def paged_cache(lengths, kv_heads, head_dim, page_size, dtype, device, seed=0, extra_pages=3):

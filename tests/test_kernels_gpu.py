@@ -438,3 +438,25 @@ def test_sample_histogram_follows_the_distribution(ops):
     expected = probs.double() * 4000
     chi2 = float(((counts - expected) ** 2 / expected).sum())
     assert chi2 < 20.5          # 4 degrees of freedom, p ~ 4e-4
+
+
+def test_a_bounded_wait_gives_up_and_leaves_the_device_usable():
+    """The product kernels wait on barriers with a time limit; when it runs out they set a status bit and
+    unwind instead of hanging.  A one-thread kernel makes that wait run out on purpose (a barrier nothing
+    arrives at, a limit of 1 ms): the launch returns, the status word says so once, and a product right
+    afterwards is exact."""
+    from aegean_tge_b200 import ops
+    ops.check_status()
+    arrived, took = ops.wait_gives_up(1_000_000)
+    torch.cuda.synchronize()
+    assert not arrived and 1_000_000 <= took < 50_000_000, (arrived, took)
+    with pytest.raises(ops.DeviceStatusError, match="wait gave up"):
+        ops.check_status()
+    ops.check_status()                                  # reading it cleared it
+    with pytest.raises(ops.KernelError):
+        ops.wait_gives_up(10**9)                        # long limits are refused outright
+    x = torch.randint(-3, 4, (24, 256), device="cuda").to(torch.bfloat16)
+    w = torch.randint(-3, 4, (384, 256), device="cuda").to(torch.bfloat16)
+    out = ops.linear(x, w, None, ops.GEMM_STORE_F32)
+    assert torch.equal(out, x.float() @ w.float().T)    # small integers: exact in bfloat16 products and float32 sums
+    ops.check_status()

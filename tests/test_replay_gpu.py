@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from conftest import ROOT, TINY
-from helpers import MODEL_TOL, rel_error
+from helpers import model_tol, rel_error
 from plain import qwen2_plain as plain
 
 pytestmark = pytest.mark.gpu
@@ -50,7 +50,7 @@ def test_trace_run_mixed_trace(model_dirs, tmp_path, name, dtype):
     _replay(model_dirs[name], dtype, steps, out_dir, max_tokens=192)     # a (128) + b (64): c reuses their pages
     vocab = config["vocab_size"]
     load = lambda s: torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{s}.f32"), dtype="<f4").reshape(-1, vocab))
-    tol = MODEL_TOL[dtype]
+    tol = model_tol(dtype, name)
     assert rel_error(load(0), ref["a"][[39]]) < tol
     assert rel_error(load(1), ref["a"][[40, 41]]) < tol
     assert rel_error(load(2), ref["b"][[38]]) < tol

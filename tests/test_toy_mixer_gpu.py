@@ -39,6 +39,9 @@ def _register():
             def state_spec(self):
                 return StateSpec((("sum", (self.hidden,)), ("count", (1,))))
 
+            def flops(self, tokens, pairs):
+                return 2.0 * tokens * self.hidden * self.hidden
+
             def forward(self, h, ctx, cache):
                 out = torch.empty_like(h)
                 begin = 0
@@ -287,3 +290,31 @@ def test_state_is_safe_under_steps_queued_ahead_and_graph_capture():
     assert stats["used"] > 0 and stats["dropped"] > 0, stats
     assert fast_engine.runner.graphs_captured >= 2 and fast_engine.runner.graph_replays > 0
     assert plain_engine.runner.graph_replays == 0 and plain_engine.stats()["steps_queued_ahead"]["used"] == 0
+
+
+def test_the_host_asks_the_model_not_the_architecture(tmp_path, capsys):
+    """``tge plan`` and the flop count behind ``tge bench prefill`` work for an architecture the package has
+    never heard of: bytes come from the parts' declared parameters and cache needs, operations from ``flops``."""
+    import json
+    from aegean_tge_b200 import cli
+    from aegean_tge_b200.bench_tools import prefill_flops
+    _register()
+    config = {"kinds": ["toy", "attention_bias", "toy"], "schedule": [0, 1, 2, 1], "architectures": ["ToyForTests"]}
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    assert cli.main(["plan", "--model", str(tmp_path), "--dtype", "float32", "--context", "128", "--sessions", "2"]) == 0
+    out = capsys.readouterr().out
+    attention = (HEADS * HD + 2 * KV * HD) * (HIDDEN + 1) + HIDDEN * HEADS * HD
+    ffn = 3 * INNER * HIDDEN
+    layers = 2 * (HIDDEN * HIDDEN + ffn + 2 * HIDDEN) + attention + ffn + 2 * HIDDEN
+    weights = 4 * (2 * VOCAB * HIDDEN + HIDDEN + layers)
+    assert f"kv       : {2 * KV * HD * 4} bytes per token; 2 x 128 tokens" in out      # one attention layer keeps pages
+    step = 4 * (VOCAB * HIDDEN + HIDDEN + layers + attention + ffn + 2 * HIDDEN)       # layer 1 is visited twice
+    assert f"decode   : {step / 2**20:.1f} MiB read per token" in out
+    engine, _ = _engine_and_weights(config, "float32")
+    assert engine.model.weight_bytes() == weights and engine.model.step_param_bytes() == step
+    assert engine.describe()["layer_kinds"] == "2 x toy_running_mean+swiglu, 1 x gqa_attention+swiglu"
+    T = 10
+    pairs = T * (T + 1) / 2
+    per_attention = 2 * T * (2 * HEADS * HD + 2 * KV * HD) * HIDDEN + 4 * HEADS * HD * pairs
+    want = 2 * (2 * T * HIDDEN * HIDDEN) + 2 * per_attention + 4 * (2 * T * ffn) + 2 * VOCAB * HIDDEN
+    assert prefill_flops(engine, T) == want
