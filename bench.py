@@ -4,13 +4,16 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
 
 One "step" is one decode step of a batch of 8 requests, each after a prompt of
-2,048 tokens (random weights, random token ids).  Prints one JSON line:
-``value`` is decoded tokens per second timed on the device over K steps,
-``e2e`` the same through the Python entry point with host tokens in and out,
-``prefill`` a 2,048-token prompt in one step against the bf16 tensor peak,
-``roofline`` the decode step against HBM bandwidth, ``points`` decode at batch
-1 and 64.  This engine runs on one GPU: for --gpus above 1 it says so and
-exits with 2.
+2,048 tokens (random weights, random token ids), with cache pages of 16 tokens
+as the benchmark configuration has them.  Prints one JSON line: ``value`` is
+decoded tokens per second timed on the device over K steps, ``e2e`` the same
+through the Python entry point with host tokens in and out, ``prefill`` a
+2,048-token prompt in one step against the bf16 tensor peak, ``roofline`` the
+decode step against HBM bandwidth.  ``points`` holds decode at batch 1 and 64
+(device-timed and end to end), a mixed step (63 decode rows beside a prompt
+portion), the same figures with the engine's default pages of 64 tokens, long
+contexts, and the 14B and 32B shapes.  This engine runs on one GPU: for --gpus
+above 1 it says so and exits with 2.
 """
 import argparse
 import json
@@ -29,6 +32,12 @@ with open(os.path.join(ROOT, "aegean-tge_b200", "config", "shapes", "qwen2.5-7b.
 PROMPT = 2048
 CONTEXT = 4096
 BATCH = 8
+PAGE = 16           # the benchmark configuration's page; the engine's own default is 64 (reported under points)
+
+
+def load_shape(name):
+    with open(os.path.join(ROOT, "aegean-tge_b200", "config", "shapes", name), "r", encoding="utf-8") as handle:
+        return json.load(handle)
 
 
 def reference_arm() -> int:
@@ -90,6 +99,56 @@ class ClockSampler:
         return {"sm_mhz": median, "sm_max_mhz": peak, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
+def end_to_end(engine, batch, steps, warmup):
+    """Decode steps through the public entry point: host token ids in, sampled ids out, every step.
+    Returns (tokens per second, host-to-device bytes per step, device-to-host bytes per step)."""
+    import time
+    import torch
+    from aegean_tge_b200.bench_tools import _random_tokens
+    vocab = engine.spec.vocab_size
+    for b in range(batch):
+        engine.add_request(_random_tokens(vocab, PROMPT, seed=2000 + b), n=warmup + steps + batch + 4)
+    while any(not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
+        engine.step()                                   # prefill and the first token, untimed
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    h2d = engine.runner.h2d_bytes_last + 8 * batch
+    d2h = engine.d2h_bytes_last
+    while engine.has_unfinished():
+        engine.step()
+    return batch * steps / seconds, h2d, d2h
+
+
+def mixed_step_ms(engine, decodes, portion, repeat=3):
+    """One step of ``decodes`` single tokens (each request holding a 2,048-token prompt) beside one prompt
+    portion of ``portion`` tokens, timed on the device."""
+    import torch
+    from aegean_tge_b200.bench_tools import _random_tokens, fill_cache
+    from aegean_tge_b200.engine.batch import Portion
+    names = fill_cache(engine, decodes, PROMPT, prefix="mixed")
+    prompt = _random_tokens(engine.spec.vocab_size, portion, seed=31)
+    times = []
+    for it in range(repeat + 1):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.runner.step([Portion(n, [7 + it], [0]) for n in names] + [Portion("mixed-prompt", prompt, [portion - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.runner.finish("mixed-prompt")
+        if it:
+            times.append(start.elapsed_time(stop))
+    for n in names:
+        engine.runner.finish(n)
+    return sum(times) / len(times)
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -98,7 +157,7 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--layers", type=int, default=CONFIG_7B["num_hidden_layers"],
                         help="fewer layers than the model has, if memory or time needs it (both numbers are reported)")
-    parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
+    parser.add_argument("--skip-points", action="store_true", help="the headline only: no points")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -108,51 +167,67 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
 
+    import gc
     import torch
     import aegean_tge_b200 as tge
     from aegean_tge_b200 import ops, peaks
-    from aegean_tge_b200.bench_tools import _random_tokens, bench_decode, bench_prefill, decode_step_bytes
-    from aegean_tge_b200.engine.scheduler import Request
+    from aegean_tge_b200.bench_tools import bench_decode, bench_prefill
 
     raw = dict(CONFIG_7B, num_hidden_layers=args.layers)
     need = args.warmup + args.steps + BATCH + 8
     most_batch = BATCH if args.skip_points else 64
-    engine = tge.Engine(random_config=raw, seed=0, dtype="bfloat16", context=CONTEXT,
-                        max_tokens=most_batch * (PROMPT + need + 64), max_batch_tokens=PROMPT, max_requests=most_batch)
-    peak, peak_source = peaks.load()
+    short = min(args.steps, 32)
 
+    def engine_for(config, page_size, batch=most_batch, context=CONTEXT, prompt=PROMPT):
+        gc.collect()
+        torch.cuda.empty_cache()
+        return tge.Engine(random_config=config, seed=0, dtype="bfloat16", context=context, page_size=page_size,
+                          max_tokens=batch * (prompt + need + 64) + (0 if args.skip_points else PROMPT),
+                          max_batch_tokens=PROMPT, max_requests=batch + 1)
+
+    engine = engine_for(raw, PAGE)
+    peak, peak_source = peaks.load()
     prefill = bench_prefill(engine, PROMPT, repeat=3, warmup=2)
 
     sampler = ClockSampler()
     sampler.start()
     main_run = bench_decode(engine, BATCH, PROMPT, steps=args.steps, warmup=args.warmup)
     clocks = sampler.stop()
-
-    # the same through the public entry point: host token ids in, sampled ids out, every step
-    vocab = engine.spec.vocab_size
-    for b in range(BATCH):
-        engine.add_request(_random_tokens(vocab, PROMPT, seed=2000 + b), n=args.warmup + args.steps + BATCH + 4)
-    while any(not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
-        engine.step()                                   # prefill and the first token, untimed
-    for _ in range(args.warmup):
-        engine.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        engine.step()
-    torch.cuda.synchronize()
-    e2e_seconds = time.perf_counter() - t0
-    h2d = engine.runner.h2d_bytes_last + 8 * BATCH
-    d2h = engine.d2h_bytes_last
-    while engine.has_unfinished():
-        engine.step()
+    e2e, h2d, d2h = end_to_end(engine, BATCH, args.steps, args.warmup)
+    queued_ahead = engine.stats()["steps_queued_ahead"]["used"]
     ops.check_status()
 
     points = {}
     if not args.skip_points:
+        rnd = lambda value, digits=1: round(value, digits)
         for batch in (1, 64):
-            points[f"decode_b{batch}"] = round(bench_decode(engine, batch, PROMPT, steps=min(args.steps, 32),
-                                                            warmup=args.warmup)["tok_s"], 1)
+            run = bench_decode(engine, batch, PROMPT, steps=short, warmup=args.warmup)
+            points[f"decode_b{batch}"] = rnd(run["tok_s"])
+            points[f"decode_b{batch}_hbm_frac"] = rnd(run["frac"], 4)
+            points[f"e2e_b{batch}"] = rnd(end_to_end(engine, batch, short, args.warmup)[0])
+        points["mixed_step_ms"] = rnd(mixed_step_ms(engine, 63, PROMPT - 63), 3)
+        del engine
+        # the engine's own default page of 64 tokens, and long contexts
+        engine = engine_for(raw, 64)
+        points["page64_prefill"] = rnd(bench_prefill(engine, PROMPT, repeat=3, warmup=2)["tok_s"])
+        for batch in (8, 64):
+            points[f"page64_decode_b{batch}"] = rnd(bench_decode(engine, batch, PROMPT, steps=short, warmup=args.warmup)["tok_s"])
+        del engine
+        for batch, context in ((4, 30000), (32, 8000)):
+            engine = engine_for(raw, 64, batch=batch, context=32768, prompt=context)
+            run = bench_decode(engine, batch, context, steps=short, warmup=args.warmup)
+            points[f"decode_b{batch}_ctx{context}"] = rnd(run["tok_s"])
+            points[f"decode_b{batch}_ctx{context}_hbm_frac"] = rnd(run["frac"], 4)
+            del engine
+        for label, shape in (("14b", "qwen2.5-14b.json"), ("32b", "qwen2.5-32b.json")):
+            engine = engine_for(load_shape(shape), PAGE, batch=BATCH)
+            if label == "14b":
+                run = bench_prefill(engine, PROMPT, repeat=3, warmup=2)
+                points["prefill_14b"], points["prefill_14b_frac"] = rnd(run["tok_s"]), rnd(run["frac"], 4)
+            run = bench_decode(engine, BATCH, PROMPT, steps=short, warmup=args.warmup)
+            points[f"decode_b8_{label}"], points[f"decode_b8_{label}_hbm_frac"] = rnd(run["tok_s"]), rnd(run["frac"], 4)
+            del engine
+        ops.check_status()
 
     line = {
         "metric": "decode tok/s at batch 8 after 2,048-token prompts; Qwen2.5-7B shape bf16 (with prefill tok/s at "
@@ -165,15 +240,14 @@ def main() -> int:
             "model": "Qwen2.5-7B shape", "layers": args.layers, "layers_of_model": CONFIG_7B["num_hidden_layers"],
             "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
             "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
-            "global_batch": BATCH, "seq_len": PROMPT, "context_limit": CONTEXT, "page_size": engine.cache.page_size,
-            "prefill_tokens": PROMPT, "parallelism": "1 GPU", "cuda_graph": engine.runner.use_graphs,
+            "global_batch": BATCH, "seq_len": PROMPT, "context_limit": CONTEXT, "page_size": PAGE,
+            "prefill_tokens": PROMPT, "parallelism": "1 GPU", "cuda_graph": True,
             "l2": "each step reads all weights (>> 126 MB L2), no flush needed",
             "peaks": peak_source,
         },
         "clocks": clocks,
-        "e2e": {"value": round(BATCH * args.steps / e2e_seconds, 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps_queued_ahead": engine.stats()["steps_queued_ahead"]["used"]},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps_queued_ahead": queued_ahead},
         "gpu_launches": main_run["launches"],
         "prefill": {"value": round(prefill["tok_s"], 1), "tokens": PROMPT, "ms": round(prefill["ms"], 3),
                     "frac": round(prefill["frac"], 4)},
