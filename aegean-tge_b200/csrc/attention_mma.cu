@@ -1155,9 +1155,9 @@ const CUtensorMap* pool_map(const void* pages, int num_pages, int kv_heads, int 
 __global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                        const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                                        int out_stride, int total_tokens, int heads, int window, int split_tokens,
-                                       int num_splits) {
+                                       int num_splits, int first_token) {
   pdl_trigger();
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int t = blockIdx.x + first_token, h = blockIdx.y;
   const int pos = positions[t];                                     // given to the step: not the previous kernel's work
   pdl_wait();
   const size_t stride = (size_t)total_tokens * heads;               // slots per split
@@ -1252,12 +1252,14 @@ TGE_API long long tge_attention_mma_scratch_floats(int tokens, int heads, int nu
 // q_start [num_seqs+1], start_pos [num_seqs], positions [tokens] are int32 on the device.
 // max_q_len / max_ctx_len are host-side bounds used only for launch geometry.
 // split_tokens: 0 = one split; else a multiple of 64 (keys per split).  scratch: see above.
-TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+// `first_token`: the sequences given here start at this token of the step (earlier tokens belong to sequences
+// that another launch serves); q, out, positions and the scratch layout stay those of the whole step.
+static int attention_dispatch(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                               const int* block_table, int max_pages, int num_pages, int page_size,
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              cudaStream_t stream) {
+                              int first_token, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && num_seqs >= 0, "attention_mma: negative sizes");
   TGE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention_mma: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
@@ -1313,9 +1315,9 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     int rc = tge_check_launch("attention_decode_tma");
     if (rc != 0) return rc;
     if (num_splits > 1) {
-      dim3 mgrid(tokens, heads);
+      dim3 mgrid(tokens - first_token, heads);
       tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1341,9 +1343,9 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
     int rc = tge_check_launch("attention_decode");
     if (rc != 0) return rc;
     if (num_splits > 1) {
-      dim3 mgrid(tokens, heads);
+      dim3 mgrid(tokens - first_token, heads);
       tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1372,16 +1374,16 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
           }
           configured_tc2 = smem2;
         }
-        const int pairs = ((tokens + p.bq - 1) / p.bq + 1) / 2 + num_seqs;
+        const int pairs = ((tokens - first_token + p.bq - 1) / p.bq + 1) / 2 + num_seqs;
         dim3 grid2(pairs * kv_heads, 1, num_splits);
         tge_launch(tc2::attention_prefill_tc2_kernel, grid2, tc2::THREADS, smem2, stream, *map_k, *map_v, p);
         int rc2 = tge_check_launch("attention_prefill_tc2");
         if (rc2 != 0) return rc2;
         if (num_splits > 1) {
-          dim3 mgrid(tokens, heads);
+          dim3 mgrid(tokens - first_token, heads);
           tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
                      (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
-                     window, p.split_tokens, num_splits);
+                     window, p.split_tokens, num_splits, first_token);
           return tge_launched("attention_merge", 2);
         }
         return 1;
@@ -1396,16 +1398,16 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
         }
         configured_tc = smem;
       }
-      const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;
+      const int tiles = (tokens - first_token + p.bq - 1) / p.bq + num_seqs;
       dim3 grid(tiles * kv_heads, 1, num_splits);
       tge_launch(tc::attention_prefill_tc_kernel, grid, tc::THREADS, smem, stream, *map_k, *map_v, p);
       int rc = tge_check_launch("attention_prefill_tc");
       if (rc != 0) return rc;
       if (num_splits > 1) {
-        dim3 mgrid(tokens, heads);
+        dim3 mgrid(tokens - first_token, heads);
         tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
                    (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
-                   window, p.split_tokens, num_splits);
+                   window, p.split_tokens, num_splits, first_token);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1421,16 +1423,16 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
         }
         configured = smem;
       }
-      const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;
+      const int tiles = (tokens - first_token + p.bq - 1) / p.bq + num_seqs;
       dim3 grid(tiles, kv_heads, num_splits);
       tge_launch(attention_prefill_tma_kernel, grid, PRE_THREADS, smem, stream, *map_k, *map_v, p);
       int rc = tge_check_launch("attention_prefill_tma");
       if (rc != 0) return rc;
       if (num_splits > 1) {
-        dim3 mgrid(tokens, heads);
+        dim3 mgrid(tokens - first_token, heads);
         tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
                    (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
-                   window, p.split_tokens, num_splits);
+                   window, p.split_tokens, num_splits, first_token);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1442,17 +1444,45 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   if (max_q_len <= 1) nwarps = group <= 16 ? 1 : (group <= 32 ? 2 : 4);
   const int rows = nwarps * 16;
   p.bq = rows / group;
-  const int tiles = (tokens + p.bq - 1) / p.bq + num_seqs;  // upper bound over any cut into portions
+  const int tiles = (tokens - first_token + p.bq - 1) / p.bq + num_seqs;  // upper bound over any cut into portions
   int rc;
   if (nwarps == 1) rc = launch<1>(p, tiles, stream);
   else if (nwarps == 2) rc = launch<2>(p, tiles, stream);
   else rc = launch<4>(p, tiles, stream);
   if (rc != 0) return rc;
   if (num_splits > 1) {
-    dim3 grid(tokens, heads);
+    dim3 grid(tokens - first_token, heads);
     tge_launch(attention_merge_kernel, grid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-        (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits);
+        (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
     return tge_launched("attention_merge", 2);
   }
   return 1;
+}
+
+// `decode_prefix`: the caller knows that the first so many sequences of a step that also holds longer portions
+// bring one token each (0: unknown or none).  They then go to the split-key decode kernel, which reads each
+// sequence's keys once for all query heads of a kv head, instead of filling one 128-row query tile of the
+// prefill kernel each; the other sequences follow in a second launch.  A row's value does not depend on the
+// route beyond rounding.
+TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                              const int* block_table, int max_pages, int num_pages, int page_size,
+                              const int* q_start, const int* start_pos, const int* positions, int num_seqs,
+                              int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
+                              int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
+                              int decode_prefix, cudaStream_t stream) {
+  TGE_REQUIRE(decode_prefix >= 0 && decode_prefix <= num_seqs, "attention_mma: %d leading single tokens of %d sequences",
+              decode_prefix, num_seqs);
+  if (decode_prefix == 0 || max_q_len <= 1 || decode_prefix == num_seqs || kv_heads <= 0 || heads / kv_heads > 16)
+    return attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start, start_pos,
+                              positions, num_seqs, tokens, max_q_len, max_ctx_len, out, out_stride, heads, kv_heads, scale,
+                              window, split_tokens, scratch, status, 0, stream);
+  const int first = attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start,
+                                       start_pos, positions, decode_prefix, decode_prefix, 1, max_ctx_len, out, out_stride,
+                                       heads, kv_heads, scale, window, split_tokens, scratch, status, 0, stream);
+  if (first < 0) return first;
+  const int rest = attention_dispatch(q, q_stride, k_pages, v_pages, block_table + (size_t)decode_prefix * max_pages, max_pages,
+                                      num_pages, page_size, q_start + decode_prefix, start_pos + decode_prefix, positions,
+                                      num_seqs - decode_prefix, tokens, max_q_len, max_ctx_len, out, out_stride, heads,
+                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, stream);
+  return rest < 0 ? rest : first + rest;
 }

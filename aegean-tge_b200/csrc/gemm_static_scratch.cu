@@ -20,7 +20,9 @@
 //  * the first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current) and keeps it; make that
 //    first call before any stream capture begins, because the look-up is not
-//    a stream operation;
+//    a stream operation.  Host threads that make their first calls at the same
+//    moment each look the address up and store the same value, which is
+//    harmless; nothing else about the entry point is shared between threads;
 //  * all calls share the one array and it keeps whatever the last call left in
 //    it.  Nothing in it has to start at zero: every partial sum that the
 //    reduction reads was written by the same call's product kernel first.  Two

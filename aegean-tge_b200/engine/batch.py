@@ -74,13 +74,17 @@ def context_from_packed(dev: torch.Tensor, host: np.ndarray, layout: "_rt.StepLa
     T, S, R = L.num_tokens, L.num_seqs, L.num_rows
     take = lambda begin, count: dev[begin:begin + count]
     q_start = host[L.q_start:L.q_start + S + 1]
+    q_lens = np.diff(q_start)
+    # decoding requests usually come first in a step (the scheduler plans running requests before new ones)
+    longer = np.flatnonzero(q_lens != 1)
+    decode_prefix = int(longer[0]) if longer.size else 0
     ctx = StepContext(
         num_tokens=T, num_seqs=S, token_ids=take(L.token_ids, T), positions=take(L.positions, T),
         seq_of_token=take(L.seq_of_token, T), q_start=take(L.q_start, S + 1), start_pos=take(L.start_pos, S),
         ctx_len=take(L.ctx_len, S), slots=take(L.slots, S),
         block_tables=[take(L.table[g], S * L.width[g]).view(S, L.width[g]) for g in range(groups)],
         max_q_len=L.max_q_len, max_ctx_len=L.max_ctx_len if max_ctx_len is None else max_ctx_len,
-        typical_ctx_len=typical_ctx_len, host_q_lens=np.diff(q_start).tolist(),
+        typical_ctx_len=typical_ctx_len, decode_prefix=decode_prefix, host_q_lens=q_lens.tolist(),
         host_start_pos=host[L.start_pos:L.start_pos + S].tolist(), host_slots=host[L.slots:L.slots + S].tolist())
     rows = take(L.logit_rows, R) if R else None
     return ctx, rows

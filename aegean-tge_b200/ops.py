@@ -110,7 +110,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.tge_last_error.restype = ctypes.c_char_p
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
-                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr])
+                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
         if lib.tge_attention_mma_head_dim() != head_dim:
@@ -535,7 +535,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               q_start: torch.Tensor, start_pos: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
               num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int, kv_heads: int, head_dim: int,
               scale: float, window: int = 0, split_tokens: int = 0, out: Optional[torch.Tensor] = None,
-              force_simt: bool = False, typical_ctx_len: int = 0) -> torch.Tensor:
+              force_simt: bool = False, typical_ctx_len: int = 0, decode_prefix: int = 0) -> torch.Tensor:
     """Paged causal attention of a flat batch of portions.
 
     q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
@@ -543,6 +543,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     every position up to each portion's last token.  Returns [T, heads*head_dim].
     ``split_tokens`` > 0 cuts the keys into runs of that many positions (a multiple of 64)
     that are attended in parallel and merged; 0 picks a value from the batch shape.
+    ``decode_prefix``: how many sequences at the head of the batch are known to bring one token each
+    while others bring more (0: unknown); the tensor-core path then serves them with its decode kernel.
     """
     _want(q, "queries", _FLOAT, contiguous=False)
     q_stride = _rows_2d(q, "queries")
@@ -574,7 +576,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                      block_table.data_ptr(), max_pages, num_pages, page_size, q_start.data_ptr(),
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
-                                     split_tokens, _ptr(scratch), status_word().data_ptr(), _stream()), lib)
+                                     split_tokens, _ptr(scratch), status_word().data_ptr(),
+                                     decode_prefix if decode_prefix >= MIN_DECODE_PREFIX else 0, _stream()), lib)
         return out
     lib = core()
     _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
@@ -583,6 +586,11 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                   head_dim, float(scale), window, int(q.dtype == torch.bfloat16),
                                   status_word().data_ptr(), _stream()), lib)
     return out
+
+
+# Fewer leading single-token sequences than this ride along in the prefill kernel: each fills one query tile,
+# which costs less than another launch.
+MIN_DECODE_PREFIX = 8
 
 
 def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int,

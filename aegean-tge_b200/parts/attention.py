@@ -116,7 +116,8 @@ class GQAttention(Mixer):
         return ops.attention(qkv[:, :self.q_dim], k_pages, v_pages, table, ctx.q_start, ctx.start_pos, ctx.positions,
                              ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads,
                              self.kv_heads, self.head_dim, self.scale, window=int(self.window or 0),
-                             split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len)
+                             split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len,
+                             decode_prefix=ctx.decode_prefix)
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         return self.ops.linear(self.attend(h, ctx, cache), self.w_o, self.b_o, self.ops.GEMM_STORE)

@@ -117,6 +117,7 @@ class StepContext:
     host_start_pos: List[int] = field(default_factory=list)
     host_slots: List[int] = field(default_factory=list)
     attn_split_tokens: int = 0         # 0 = let the kernel wrapper decide
+    decode_prefix: int = 0             # in a step with longer portions: how many leading portions are single tokens
     scratch: Dict[str, Any] = field(default_factory=dict)
 
 

@@ -293,11 +293,70 @@ def test_rope_kv_store(ops, dtype, heads, kv_heads, head_dim, rotary):
     assert torch.equal(k_pages[~touched], before_k[~touched]), "a slot outside the step's positions was written"
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,hidden", [(7, 1, 128, 128, 512), (4, 2, 128, 0, 256), (6, 2, 64, 64, 384),
+                                                                 (5, 1, 64, 32, 320)])
+@pytest.mark.parametrize("q_lens,starts", [([1, 1, 1], [30, 47, 0]), ([5, 1, 20], [30, 47, 0]), ([70, 58], [3, 16])])
+@pytest.mark.parametrize("deferred", [False, True])
+def test_linear_qkv_rope_store(ops, heads, kv_heads, head_dim, rotary, hidden, q_lens, starts, deferred):
+    """The q/k/v product fused with bias, rotation and the cache store, for small batches (one kernel adds the
+    product's partial sums, rotates and stores) and larger ones (separate kernels), with rows that still lack
+    their norm factor and with complete ones, at two head sizes, with a full, a partial and no rotation."""
+    from aegean_tge_b200.parts.rope import rotary_tables
+    page_size = 16
+    positions, seq_of_token, _, _ = batch_index(q_lens, starts, DEV)
+    T = sum(q_lens)
+    width = (heads + 2 * kv_heads) * head_dim
+    gen = torch.Generator().manual_seed(heads * 10 + head_dim + T)
+    x = torch.randn(T, hidden, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(width, hidden, generator=gen) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(width, generator=gen)
+    lengths = [s + n for s, n in zip(starts, q_lens)]
+    cos = sin = None
+    if rotary:
+        cos, sin = rotary_tables(12345.0, rotary, 96)
+    taken = x
+    normed = x.double()
+    if deferred and T <= 128:
+        # rows = stream * gain in bfloat16 plus the sums of squares of the stream in slices: what linear_add_norm hands on
+        stream = torch.randn(T, hidden, generator=gen) * 2.0
+        gain = 1.0 + 0.2 * torch.randn(hidden, generator=gen)
+        rows = (stream * gain).to(torch.bfloat16)
+        slices = -(-hidden // 96)
+        sums = torch.stack([(stream[:, i * 96:(i + 1) * 96].double() ** 2).sum(1) for i in range(slices)]).float()
+        taken = ops.DeferredRows(rows.to(DEV), sums.to(DEV).contiguous(), hidden, 1e-5)
+        normed = rows.double() / torch.sqrt((stream.double() ** 2).mean(1, keepdim=True) + 1e-5)
+    qkv_ref = ops_plain.linear(normed, w, bias)
+    pos = positions.cpu().long()
+    q = qkv_ref[:, :heads * head_dim].view(T, heads, head_dim)
+    k = qkv_ref[:, heads * head_dim:(heads + kv_heads) * head_dim].view(T, kv_heads, head_dim)
+    v = qkv_ref[:, (heads + kv_heads) * head_dim:].view(T, kv_heads, head_dim)
+    c = cos[pos] if rotary else None
+    s = sin[pos] if rotary else None
+    q_ref, k_ref = ops_plain.rotate_half(q, c, s, rotary), ops_plain.rotate_half(k, c, s, rotary)
+    for _ in range(1):
+        k_pages, v_pages, table, _, _ = paged_cache(lengths, kv_heads, head_dim, page_size, torch.bfloat16, DEV, seed=4)
+        before_k = k_pages.clone()
+        out = ops.linear_qkv_rope_store(taken if not isinstance(taken, torch.Tensor) else taken.to(DEV), w.to(DEV),
+                                        bias.to(DEV), None if cos is None else cos.to(DEV),
+                                        None if sin is None else sin.to(DEV), rotary, positions, seq_of_token, table,
+                                        k_pages, v_pages, heads, kv_heads, head_dim)
+        ops.check_status()
+        assert rel_error(out[:, :heads * head_dim].reshape(T, heads, head_dim), q_ref) < TOL[torch.bfloat16]
+        touched = torch.zeros_like(before_k, dtype=torch.bool)
+        for t in range(T):
+            page = int(table[int(seq_of_token[t]), int(pos[t]) // page_size])
+            slot = int(pos[t]) % page_size
+            assert rel_error(k_pages[page, :, slot], k_ref[t]) < TOL[torch.bfloat16]
+            assert rel_error(v_pages[page, :, slot], v[t]) < TOL[torch.bfloat16]
+            touched[page, :, slot] = True
+        assert torch.equal(k_pages[~touched], before_k[~touched]), "a slot outside the step's positions was written"
+
+
 # ---------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------
 def _attention_case(ops, dtype, heads, kv_heads, head_dim, q_lens, starts, window=0, split=0, force_simt=False,
-                    page_size=16, spike=None):
+                    page_size=16, spike=None, decode_prefix=0):
     lengths = [s + n for s, n in zip(starts, q_lens)]
     k_pages, v_pages, table, k_list, v_list = paged_cache(lengths, kv_heads, head_dim, page_size, dtype, DEV, seed=9)
     positions, seq_of_token, q_start, start_pos = batch_index(q_lens, starts, DEV)
@@ -315,7 +374,7 @@ def _attention_case(ops, dtype, heads, kv_heads, head_dim, q_lens, starts, windo
     dq = buf.to(DEV)
     out = ops.attention(dq[:, :heads * head_dim], k_pages, v_pages, table, q_start, start_pos, positions,
                         seq_of_token, len(q_lens), max(q_lens), max(lengths), heads, kv_heads, head_dim, scale,
-                        window=window, split_tokens=split, force_simt=force_simt)
+                        window=window, split_tokens=split, force_simt=force_simt, decode_prefix=decode_prefix)
     ops.check_status()
     q = buf[:, :heads * head_dim].view(T, heads, head_dim)
     refs = []
@@ -333,6 +392,23 @@ def test_attention_simt(ops, dtype, heads, kv_heads, head_dim):
     err, _, _ = _attention_case(ops, dtype, heads, kv_heads, head_dim, [5, 1, 37, 2], [30, 150, 0, 63],
                                 force_simt=True)
     assert err < TOL[dtype]
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(7, 1, 128), (28, 4, 64), (6, 2, 48), (40, 2, 16)])
+@pytest.mark.parametrize("page_size,split", [(16, 0), (64, 128), (4, 64)])
+def test_attention_routes_leading_single_tokens_to_the_decode_kernel(ops, heads, kv_heads, head_dim, page_size, split):
+    """A step whose first ten sequences bring one token each and whose last two bring portions: told so, the
+    tensor-core path serves the ten with its decode kernel and the rest with its prefill kernel (with and without
+    a cut of the keys, whose partial results share one scratch buffer); untold, one kernel serves all.  Both are
+    right, and they agree to rounding.  One single token sits at position 0, one far into its sequence."""
+    q_lens = [1] * 10 + [70, 3]
+    starts = [0, 199, 64, 5, 130, 17, 63, 64, 255, 1] + [200, 15]
+    routed, out_routed, _ = _attention_case(ops, torch.bfloat16, heads, kv_heads, head_dim, q_lens, starts, split=split,
+                                            page_size=page_size, decode_prefix=10)
+    plain_way, out_plain, _ = _attention_case(ops, torch.bfloat16, heads, kv_heads, head_dim, q_lens, starts, split=split,
+                                              page_size=page_size)
+    assert routed < TOL[torch.bfloat16] and plain_way < TOL[torch.bfloat16]
+    assert rel_error(out_routed, out_plain.float()) < TOL[torch.bfloat16]
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim", [(6, 2, 48), (3, 1, 32), (4, 4, 16), (7, 1, 128), (28, 4, 64),

@@ -17,7 +17,7 @@ from helpers import TOL, rel_error
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32 = 0, 1, 2
+GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32, GEMM_SWIGLU = 0, 1, 2, 3
 
 
 def _symbol():
@@ -59,6 +59,46 @@ def test_static_scratch_matches_the_regular_entry_point_twice_in_a_row():
         assert rel_error(got, expected) < TOL[torch.float32]
         assert rel_error(got, (x.double() @ w.double().T + bias.double()
                                + (start.double() if epilogue == GEMM_ADD_F32 else 0.0))) < TOL[torch.float32]
+
+
+def test_static_scratch_with_the_other_epilogues_and_the_two_sm_plan():
+    """The reductions that read the shared buffer in other ways: the gated epilogue (pairs of partial sums), the
+    bfloat16 store, and a product of more than 128 tokens that pairs two SMs on a tile and still cuts along k."""
+    ops, lib, fn = _symbol()
+    status = ops.status_word()
+    gen = torch.Generator().manual_seed(22)
+    plan = (ctypes.c_int * 4)()
+    lib.tge_gemm_tcgen05_describe.restype = None
+    lib.tge_gemm_tcgen05_describe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    paired = None
+    for M, N, K in ((160, 512, 4096), (192, 768, 8192), (256, 512, 8192), (144, 256, 16384)):
+        lib.tge_gemm_tcgen05_describe(M, N, K, plan)
+        if plan[0] == 1 and plan[3] > 1 and lib.tge_gemm_tcgen05_scratch_floats(M, N, K) <= 4 * 1024 * 1024:
+            paired = (M, N, K)
+            break
+    cases = [(8, 512, 2048, GEMM_SWIGLU), (24, 384, 3584, GEMM_STORE)]
+    if paired is not None:          # (the pair kernel can be switched off by the environment; then there is no such plan)
+        cases.append((*paired, GEMM_STORE_F32))
+    for M, N, K, epilogue in cases:
+        assert lib.tge_gemm_tcgen05_scratch_floats(M, N, K) > 0
+        x = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(DEV)
+        w = (torch.randn(N, K, generator=gen) * 0.05).to(torch.bfloat16).to(DEV)
+        bias = None if epilogue == GEMM_SWIGLU else torch.randn(N, generator=gen).to(DEV)
+        shape = (M, N // 2) if epilogue == GEMM_SWIGLU else (M, N)
+        dtype = torch.float32 if epilogue == GEMM_STORE_F32 else torch.bfloat16
+        expected = ops.linear(x, w, bias, epilogue)
+        got = torch.zeros(shape, dtype=dtype, device=DEV)
+        rc = _call(fn, x, w, bias, got, epilogue, status)
+        assert rc == 2, lib.tge_last_error()
+        ops.check_status()
+        assert torch.equal(got, expected)                 # the same kernels, the same order of sums
+        product = x.double() @ w.double().T
+        if epilogue == GEMM_SWIGLU:
+            gate, up = product[:, 0::2], product[:, 1::2]
+            reference = gate / (1.0 + torch.exp(-gate)) * up
+        else:
+            reference = product + bias.double()
+        assert rel_error(got, reference) < TOL[dtype]
 
 
 def test_static_scratch_refuses_what_does_not_fit():
