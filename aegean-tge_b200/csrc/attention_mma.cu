@@ -51,6 +51,7 @@ struct AttnParams {
   int q_stride, out_stride;
   int max_pages, num_pages, page_size, page_shift;
   int num_seqs, total_tokens;
+  int early_tiles;           // decode: key tiles of settled positions asked for before the dependency wait (0: none)
   int heads, kv_heads, group, bq;
   int window, split_tokens, num_splits;
   float scale_log2;
@@ -639,8 +640,8 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   __syncthreads();
   // All of the above read only what the step was given (lengths, the block table), which no kernel of the step
   // writes: it ran while the kernel before this one finished.  The queries and the newest keys and values are
-  // that kernel's work.
-  pdl_wait();
+  // that kernel's work; the keys and values of earlier positions are earlier steps' work, so the loading warp
+  // asks for a ring of those tiles first and only then waits for the kernel before this one.
 
   const int pages_per_tile = BKV >> p.page_shift;
   auto issue = [&](int tile) {                                          // the loading warp's first lane only
@@ -669,13 +670,19 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
     // The loading warp runs ahead of the others by up to a ring of tiles; nobody waits for anybody else
     // block-wide.  A stage is refilled once all computing warps have released it.
     if (elect_one()) {
-      for (int tile = 0; tile < num_tiles; ++tile) {
+      // tiles that end before this step's own position hold nothing this step writes
+      const int settled = pos >= k_first ? (pos - k_first) / BKV : 0;
+      int tile = 0;
+      for (; tile < num_tiles && tile < p.early_tiles && tile < settled; ++tile) issue(tile);
+      pdl_wait();
+      for (; tile < num_tiles; ++tile) {
         if (tile >= DEC_STAGES)
           mbar_wait_bounded(empty_bar(tile % DEC_STAGES), (uint32_t)(tile / DEC_STAGES - 1) & 1u, p.status);
         issue(tile);
       }
     }
   }
+  pdl_wait();
 
   uint32_t qf[HD / 16][4];
 #pragma unroll
@@ -1281,6 +1288,8 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.num_seqs = num_seqs; p.total_tokens = tokens;
+  static const bool early = getenv("TGE_NO_EARLY_KV") == nullptr || getenv("TGE_NO_EARLY_KV")[0] == '\0';
+  p.early_tiles = early ? DEC_STAGES : 0;
   p.heads = heads; p.kv_heads = kv_heads; p.group = group;
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
