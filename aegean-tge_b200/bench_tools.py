@@ -104,10 +104,32 @@ def bench_decode(engine, batch: int, prompt_len: int, steps: int = 64, warmup: i
             "launches": ops.launches - launches_before, "steps": steps}
 
 
-def step_timeline(engine, batch: int, prompt_len: int, prefill: bool) -> List[Dict[str, float]]:
+def bench_mixed(engine, decodes: int, prompt_len: int, portion: int, repeat: int = 3) -> Dict[str, float]:
+    """One step of ``decodes`` single tokens (each request holding ``prompt_len`` tokens) beside one prompt
+    portion of ``portion`` tokens, timed on the device: what a scheduler's step looks like while a prompt arrives."""
+    names = fill_cache(engine, decodes, prompt_len, prefix="mixed")
+    prompt = _random_tokens(engine.spec.vocab_size, portion, seed=31)
+    times = []
+    for it in range(repeat + 1):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.runner.step([Portion(n, [7 + it], [0]) for n in names] + [Portion("mixed-prompt", prompt, [portion - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.runner.finish("mixed-prompt")
+        if it:
+            times.append(start.elapsed_time(stop))
+    for n in names:
+        engine.runner.finish(n)
+    ms = sum(times) / len(times)
+    return {"ms": ms, "decodes": decodes, "portion": portion, "tok_s": (decodes + portion) / (ms * 1e-3)}
+
+
+def step_timeline(engine, batch: int, prompt_len: int, prefill: bool, portion: int = 0) -> List[Dict[str, float]]:
     """Where one step's time goes, by kernel name, from the CUDA activity records of one step after
     warm-up: a prompt of ``prompt_len`` tokens (``prefill``) or one token for each of ``batch`` requests
-    that hold ``prompt_len`` tokens.
+    that hold ``prompt_len`` tokens, with ``portion`` > 0 beside one prompt portion of that many tokens.
 
     A kernel launched as the dependent of another starts early and waits, so its own duration says
     little.  What is charged to a kernel here is the time from the end of the kernel that ended before it
@@ -125,9 +147,13 @@ def step_timeline(engine, batch: int, prompt_len: int, prefill: bool) -> List[Di
         names = []
     else:
         names = fill_cache(engine, batch, prompt_len, prefix="timeline")
+        beside = _random_tokens(vocab, portion, seed=78) if portion > 0 else []
 
         def run():
-            engine.runner.step([Portion(n, [5], [0]) for n in names])
+            engine.runner.step([Portion(n, [5], [0]) for n in names] +
+                               ([Portion("timeline-portion", beside, [portion - 1])] if portion > 0 else []))
+            if portion > 0:
+                engine.runner.finish("timeline-portion")
     for _ in range(4):
         run()
     torch.cuda.synchronize()

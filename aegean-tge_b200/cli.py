@@ -5,6 +5,7 @@
     tge generate --model DIR --tokens "a b c" [--n N] [--temp T] [--top-k N] [--top-p P] [--min-p P]
                  [--repeat-penalty R] [--penalty-window N] [--seed N] [--context N] [--print-ids]
     tge bench prefill|decode --model DIR [--prompt-len N] [--batch B] [--n N] [--repeat R]
+    tge bench mixed --model DIR [--batch B] [--prompt-len N] [--portion P]      (B single tokens beside a prompt portion)
     tge fidelity --model DIR [--context N] [--tokens N] [--corpus FILE]
     tge bench continuous --model DIR [--requests N] [--tokens N] [--sequences N] [--prompt-tokens N] [--prompt-max N]
     tge make-random --config FILE --out DIR [--seed S] [--dtype float32|bfloat16]
@@ -87,13 +88,15 @@ def build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--print-ids", action="store_true", help="print generated token ids")
     generate.add_argument("--text", action="store_true", help="(needs a tokenizer: not supported)")
     bench = commands.add_parser("bench", help="prefill or decode throughput with its roofline fraction")
-    bench.add_argument("what", choices=["prefill", "decode", "continuous"])
+    bench.add_argument("what", choices=["prefill", "decode", "mixed", "continuous"])
     _model_args(bench)
     bench.add_argument("--prompt-len", type=int, default=2048)
     bench.add_argument("--batch", type=int, default=1)
     bench.add_argument("--n", type=int, default=64, help="decode steps to time")
     bench.add_argument("--repeat", type=int, default=3)
-    bench.add_argument("--timeline", action="store_true", help="prefill/decode: also list one step's kernels with their device times")
+    bench.add_argument("--portion", type=int, default=1985,
+                       help="mixed: tokens of the prompt portion that runs beside --batch single tokens (default 1985)")
+    bench.add_argument("--timeline", action="store_true", help="prefill/decode/mixed: also list one step's kernels with their device times")
     # bench continuous, with the reference's names (apps/cli/main.cpp:2825-2890)
     bench.add_argument("--requests", type=int, default=8, help="continuous: requests to serve (default 8)")
     bench.add_argument("--tokens", type=int, default=32, help="continuous: tokens generated per request (default 32)")
@@ -390,7 +393,12 @@ def command_bench(args) -> int:
     if args.what == "continuous":
         return command_bench_continuous(args)
     engine = _engine_from(args)
-    if args.what == "prefill":
+    if args.what == "mixed":
+        from .bench_tools import bench_mixed
+        result = bench_mixed(engine, args.batch, args.prompt_len, args.portion, repeat=args.repeat)
+        print(f"mixed    : {result['decodes']} single tokens at context {args.prompt_len} beside a portion of "
+              f"{result['portion']} tokens: {result['ms']:.3f} ms/step ({result['tok_s']:.1f} tok/s)")
+    elif args.what == "prefill":
         result = bench_prefill(engine, args.prompt_len, repeat=args.repeat)
         print(f"prefill  : {result['tokens']} tokens in {result['ms']:.2f} ms ({result['tok_s']:.1f} tok/s), "
               f"{result['tflops']:.1f} TFLOP/s = {result['frac']:.3f} of {result['peak_tflops']:.0f} ({result['peak_source']})")
@@ -402,7 +410,8 @@ def command_bench(args) -> int:
     if args.timeline:
         from .bench_tools import step_timeline
         print("one step's time by kernel (each charged from the end of the kernel before it to its own end):")
-        for row in step_timeline(engine, args.batch, args.prompt_len, args.what == "prefill"):
+        for row in step_timeline(engine, args.batch, args.prompt_len, args.what == "prefill",
+                                 portion=args.portion if args.what == "mixed" else 0):
             print(f"  {row['us']:9.1f} us  {100 * row['share']:5.1f} %  x{row['launches']:<4d} {row['kernel']}")
     return 0
 

@@ -3,6 +3,7 @@
     python -m aegean_tge_b200.kernel_cases gemm --m 2048 --n 9472 --k 3584 --epilogue swiglu
     python -m aegean_tge_b200.kernel_cases attention --batch 64 --context 2048 --q-len 1
     python -m aegean_tge_b200.kernel_cases attention --batch 1 --context 2048 --q-len 2048
+    python -m aegean_tge_b200.kernel_cases fill --elements 545000000
 
 Weights are rotated between launches so that a launch never finds them in L2; attention reads a
 freshly shuffled page table.  Sizes default to the Qwen2.5-7B layer shapes.
@@ -76,6 +77,22 @@ def run_attention(args) -> None:
           f"K/V {kv_bytes / 1e6:.1f} MB at {kv_bytes / us / 1e3:.0f} GB/s, {flops / us / 1e6:.1f} TFLOP/s")
 
 
+def run_fill(args) -> None:
+    """The random-weights kernel writing one bfloat16 tensor (the default: an embedding table of the 7B shape)."""
+    from .weights import normal, random_tensor
+    times = []
+    for i in range(args.repeat):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        tensor = random_tensor(f"tensor.{i}", (args.elements,), normal(0.02), 0, torch.bfloat16, torch.device("cuda:0"))
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop) * 1e3)
+        del tensor
+    us = sorted(times[1:])[len(times[1:]) // 2]
+    print(f"fill {args.elements} bfloat16 elements: {us:.1f} us, written at {args.elements * 2 / us / 1e3:.0f} GB/s")
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="kernel_cases", description=__doc__.split("\n\n")[0])
     sub = parser.add_subparsers(dest="what", required=True)
@@ -97,9 +114,14 @@ def main(argv=None) -> int:
     attn.add_argument("--page-size", type=int, default=64)
     attn.add_argument("--split", type=int, default=0, help="keys per split (a multiple of 64); 0 lets the wrapper choose")
     attn.add_argument("--repeat", type=int, default=8)
+    fill = sub.add_parser("fill")
+    fill.add_argument("--elements", type=int, default=152064 * 3584)
+    fill.add_argument("--repeat", type=int, default=5)
     args = parser.parse_args(argv)
     if args.what == "gemm":
         run_gemm(args)
+    elif args.what == "fill":
+        run_fill(args)
     else:
         run_attention(args)
     ops.check_status()

@@ -125,30 +125,6 @@ def end_to_end(engine, batch, steps, warmup):
     return batch * steps / seconds, h2d, d2h
 
 
-def mixed_step_ms(engine, decodes, portion, repeat=3):
-    """One step of ``decodes`` single tokens (each request holding a 2,048-token prompt) beside one prompt
-    portion of ``portion`` tokens, timed on the device."""
-    import torch
-    from aegean_tge_b200.bench_tools import _random_tokens, fill_cache
-    from aegean_tge_b200.engine.batch import Portion
-    names = fill_cache(engine, decodes, PROMPT, prefix="mixed")
-    prompt = _random_tokens(engine.spec.vocab_size, portion, seed=31)
-    times = []
-    for it in range(repeat + 1):
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        start.record()
-        engine.runner.step([Portion(n, [7 + it], [0]) for n in names] + [Portion("mixed-prompt", prompt, [portion - 1])])
-        stop.record()
-        torch.cuda.synchronize()
-        engine.runner.finish("mixed-prompt")
-        if it:
-            times.append(start.elapsed_time(stop))
-    for n in names:
-        engine.runner.finish(n)
-    return sum(times) / len(times)
-
-
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -171,7 +147,7 @@ def main() -> int:
     import torch
     import aegean_tge_b200 as tge
     from aegean_tge_b200 import ops, peaks
-    from aegean_tge_b200.bench_tools import bench_decode, bench_prefill
+    from aegean_tge_b200.bench_tools import bench_decode, bench_mixed, bench_prefill
 
     raw = dict(CONFIG_7B, num_hidden_layers=args.layers)
     need = args.warmup + args.steps + BATCH + 8
@@ -205,7 +181,7 @@ def main() -> int:
             points[f"decode_b{batch}"] = rnd(run["tok_s"])
             points[f"decode_b{batch}_hbm_frac"] = rnd(run["frac"], 4)
             points[f"e2e_b{batch}"] = rnd(end_to_end(engine, batch, short, args.warmup)[0])
-        points["mixed_step_ms"] = rnd(mixed_step_ms(engine, 63, PROMPT - 63), 3)
+        points["mixed_step_ms"] = rnd(bench_mixed(engine, 63, PROMPT, PROMPT - 63)["ms"], 3)
         del engine
         # the engine's own default page of 64 tokens, and long contexts
         engine = engine_for(raw, 64)
