@@ -153,7 +153,7 @@ def to_bfloat16(x: np.ndarray) -> np.ndarray:
 
 def qwen2_plan(config: dict) -> Iterator[Tuple[str, Tuple[int, ...], str, Tuple]]:
     """(name, shape, role, draw) of a Qwen2.5 checkpoint: matrices and biases N(0, 0.02), norm weights
-    1 + U(-0.1, 0.1) (the configurations of this build's task statement)."""
+    1 + U(-0.1, 0.1) (what the engine's random-weights mode draws for this architecture)."""
     h, ff, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
     heads = config["num_attention_heads"]
     kv_heads = config.get("num_key_value_heads") or heads

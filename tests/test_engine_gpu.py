@@ -417,3 +417,25 @@ def test_steps_queued_ahead_change_nothing(model_dirs, tmp_path):
     assert "end_token" in reasons
     ahead, reasons_ahead, counts = run(str(folder), True)
     assert ahead == plain and reasons_ahead == reasons and counts["dropped"] >= 1 and counts["used"] > 5
+
+
+def test_decode_graphs_are_capped_and_share_a_pool(model_dirs, oracle):
+    """Decode steps at many batch sizes capture a graph each; only the most recently used ones are kept, they
+    allocate from one pool, and a graph that was dropped is simply captured again: the logits stay those of the
+    plain model whichever graphs live."""
+    name, dtype = "D", "float32"
+    engine = _engine(model_dirs, name, dtype, max_requests=6)
+    engine.runner.max_graphs = 2
+    prompts = [_tokens(name, 6 + i, salt=300 + i) for i in range(5)]
+    nexts = [_tokens(name, 6, salt=400 + i) for i in range(5)]
+    engine.runner.step([_portion(i, prompts[i], []) for i in range(5)])
+    done = [0] * 5
+    for batch in (1, 2, 3, 1, 4, 2):                              # 1 and 2 come back after they were dropped
+        rows = engine.runner.step([_portion(i, [nexts[i][done[i]]]) for i in range(batch)])
+        for i in range(batch):
+            done[i] += 1
+            ref = oracle(name, prompts[i] + nexts[i][:done[i]])[-1]
+            assert rel_error(rows[i], ref) < model_tol(dtype, name), (batch, i)
+        assert len(engine.runner._graphs) <= 2
+    assert engine.runner.graphs_captured == 6 and engine.runner.graph_replays == 6
+    assert engine.runner._graph_pool is not None

@@ -395,18 +395,20 @@ def test_attention_simt(ops, dtype, heads, kv_heads, head_dim):
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim", [(7, 1, 128), (28, 4, 64), (6, 2, 48), (40, 2, 16)])
-@pytest.mark.parametrize("page_size,split", [(16, 0), (64, 128), (4, 64)])
-def test_attention_routes_leading_single_tokens_to_the_decode_kernel(ops, heads, kv_heads, head_dim, page_size, split):
+@pytest.mark.parametrize("page_size,split,window", [(16, 0, 0), (64, 128, 0), (4, 64, 0), (16, 0, 40), (32, 64, 100)])
+def test_attention_routes_leading_single_tokens_to_the_decode_kernel(ops, heads, kv_heads, head_dim, page_size, split,
+                                                                     window):
     """A step whose first ten sequences bring one token each and whose last two bring portions: told so, the
     tensor-core path serves the ten with its decode kernel and the rest with its prefill kernel (with and without
     a cut of the keys, whose partial results share one scratch buffer); untold, one kernel serves all.  Both are
-    right, and they agree to rounding.  One single token sits at position 0, one far into its sequence."""
+    right, and they agree to rounding.  One single token sits at position 0, one far into its sequence; with a
+    window some splits hold no visible key."""
     q_lens = [1] * 10 + [70, 3]
     starts = [0, 199, 64, 5, 130, 17, 63, 64, 255, 1] + [200, 15]
     routed, out_routed, _ = _attention_case(ops, torch.bfloat16, heads, kv_heads, head_dim, q_lens, starts, split=split,
-                                            page_size=page_size, decode_prefix=10)
+                                            page_size=page_size, decode_prefix=10, window=window)
     plain_way, out_plain, _ = _attention_case(ops, torch.bfloat16, heads, kv_heads, head_dim, q_lens, starts, split=split,
-                                              page_size=page_size)
+                                              page_size=page_size, window=window)
     assert routed < TOL[torch.bfloat16] and plain_way < TOL[torch.bfloat16]
     assert rel_error(out_routed, out_plain.float()) < TOL[torch.bfloat16]
 

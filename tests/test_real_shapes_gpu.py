@@ -1,7 +1,7 @@
 """The engine at real layer sizes against the plain implementation.
 
 Two layers of the Qwen2.5-7B, 14B and 32B shapes (the widths, head counts, inner widths and the whole
-152,064-row vocabulary of this build's task configurations), random weights from the seed on both sides:
+152,064-row vocabulary of the Qwen2.5 models), random weights from the seed on both sides:
 the engine draws them on the device, the oracle with the tests' own numpy restatement of the generator.
 The oracle is tests/plain/qwen2_plain.py in float64.  To keep it in seconds it computes the logits of a
 few runs of vocabulary rows only (the first rows, a run in the middle that starts at an odd row, and the
