@@ -132,7 +132,6 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   // every kv head start first and the short ones fill the gaps (with the kv head as blockIdx.y, a whole kv
   // head's long tiles started only after the first ones' short tiles).
   const int kvh = (int)blockIdx.x % p.kv_heads, tile_rank = (int)blockIdx.x / p.kv_heads, split = blockIdx.z;
-  pdl_wait();
   if (tid == 0) {
     int total = 0;
     for (int s = 0; s < p.num_seqs; ++s) total += (p.q_start[s + 1] - p.q_start[s] + p.bq - 1) / p.bq;
@@ -181,6 +180,9 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
   const int row_token = q_begin + q_first + (row_valid ? qi : 0);
   const int row_pos = pos0 + qi;
   const int row_head = kvh * p.group + gg;
+  // Everything above read what the step was given (lengths, positions, the block table) and cleared this block's own
+  // shared memory, while the kernel before this one was still running; the queries and the newest keys are its work.
+  pdl_wait();
   if (tid < ROWS) {
     // Q row into the K-major swizzled tile: 64-column blocks of [128 rows][128 bytes]
     const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)row_token * p.q_stride + (size_t)row_head * HD);

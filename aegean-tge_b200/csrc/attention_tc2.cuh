@@ -67,7 +67,6 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc2_kernel(
 
   const int tid = threadIdx.x, lane = tid & 31, warp = uniform_warp_index();
   const int kvh = (int)blockIdx.x % p.kv_heads, pair_rank = (int)blockIdx.x / p.kv_heads, split = blockIdx.z;
-  pdl_wait();
   if (tid == 0) {
     // a block takes two consecutive tiles of queries of one request; long ones first
     int total = 0;
@@ -119,6 +118,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_tc2_kernel(
   const int row_token = q_begin + q_first + (row_valid ? q_in_pair : 0);
   const int row_pos = pos0 + q_in_pair;
   const int row_head = kvh * p.group + gg;
+  // Everything above read what the step was given (lengths, positions, the block table) and cleared this block's own
+  // shared memory, while the kernel before this one was still running; the queries and the newest keys are its work.
+  pdl_wait();
   if (warp < SOFTMAX_WARPS) {
     // Q row into the K-major swizzled tile of its query tile: 64-column blocks of [128 rows][128 bytes]
     const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)row_token * p.q_stride + (size_t)row_head * HD);
