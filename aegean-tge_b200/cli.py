@@ -399,9 +399,11 @@ def command_bench(args) -> int:
         print(f"mixed    : {result['decodes']} single tokens at context {args.prompt_len} beside a portion of "
               f"{result['portion']} tokens: {result['ms']:.3f} ms/step ({result['tok_s']:.1f} tok/s)")
     elif args.what == "prefill":
-        result = bench_prefill(engine, args.prompt_len, repeat=args.repeat)
+        result = bench_prefill(engine, args.prompt_len, repeat=args.repeat, sustain_seconds=1.0)
         print(f"prefill  : {result['tokens']} tokens in {result['ms']:.2f} ms ({result['tok_s']:.1f} tok/s), "
               f"{result['tflops']:.1f} TFLOP/s = {result['frac']:.3f} of {result['peak_tflops']:.0f} ({result['peak_source']})")
+        print(f"           after a pause {result['burst_ms']:.2f} ms = {result['burst_frac']:.3f} of the burst peak; "
+              f"sustained {result['sustained_ms']:.2f} ms = {result['sustained_frac']:.3f} of the sustained peak")
     else:
         result = bench_decode(engine, args.batch, args.prompt_len, steps=args.n)
         print(f"decode   : batch {args.batch} at context {args.prompt_len}: {result['ms_per_step']:.3f} ms/step "
