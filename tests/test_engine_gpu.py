@@ -439,3 +439,19 @@ def test_decode_graphs_are_capped_and_share_a_pool(model_dirs, oracle):
         assert len(engine.runner._graphs) <= 2
     assert engine.runner.graphs_captured == 6 and engine.runner.graph_replays == 6
     assert engine.runner._graph_pool is not None
+
+
+def test_command_line_generates_and_benches(model_dirs, capsys):
+    """`tge generate` and the three single-step benches on a tiny model: exit codes and the labels of their lines."""
+    from aegean_tge_b200.cli import main
+    assert main(["generate", "--model", model_dirs["D"], "--tokens", "5 17 3", "--n", "6", "--print-ids", "--context", "128"]) == 0
+    out = capsys.readouterr().out
+    assert "prefill  :" in out and "decode   :" in out and len(out.split("ids      :")[1].split()) == 6
+    common = ["--model", model_dirs["D"], "--context", "512", "--max-requests", "12", "--page-size", "16"]
+    assert main(["bench", "decode", *common, "--batch", "3", "--prompt-len", "40", "--n", "4"]) == 0
+    assert main(["bench", "prefill", *common, "--prompt-len", "100", "--repeat", "1"]) == 0
+    assert main(["bench", "mixed", *common, "--batch", "9", "--prompt-len", "40", "--portion", "70", "--timeline"]) == 0
+    out = capsys.readouterr().out
+    assert "decode   : batch 3 at context 40" in out and "after a pause" in out
+    assert "mixed    : 9 single tokens at context 40 beside a portion of 70 tokens" in out
+    assert "attention_decode" in out and "span of the step" in out           # the nine single tokens took the decode kernel
