@@ -206,7 +206,8 @@ class Engine:
         for item in plan.items:
             self.cache.set_computed(item.request.id, item.start + item.count)
         states = [r.rng.state for r in requests]
-        snapshot = self.cache.snapshot_state([self.cache.slot_of(name) for name in names])
+        snapshot = (self.cache.snapshot_state([self.cache.slot_of(name) for name in names])
+                    if self.cache.state_storage else None)
         try:
             logits = self.runner.step_ahead(names, ids)
         except PoolExhausted:
