@@ -11,14 +11,25 @@
 // share of the total reaches top_p; the draw u scales the kept mass and the walk over the kept
 // prefix returns the first candidate at which the running remainder is <= 0.
 //
-// The order is produced by a bitonic sort of (probability, index) pairs in scratch memory in
-// global memory (a power of two >= vocab entries per row, padded with -1); sums over the sorted
-// prefix are formed per thread over contiguous chunks and combined in chunk order.
+// Only a prefix of the order is ever walked, and with the distributions a language model makes it is short
+// (a top-k of tens, a nucleus of hundreds among 150,000 tokens).  So the kernel first narrows a threshold on the
+// probabilities' bit patterns in three counting passes (ten coarse levels 2^-4, 2^-8, ... of the best while the
+// probabilities are computed; then the four exponents of the level; then eight steps of the mantissa), each time
+// taking the highest threshold whose candidates are certain to contain the prefix (they hold the top k; or their
+// mass reaches the nucleus's share of the total; or they are all that min-p keeps), gathers the candidates, at
+// most 16,384, into shared memory and sorts those.  A row whose prefix cannot be bounded that way (a flat distribution under
+// top-p) takes the old way: a bitonic sort of all (probability, index) pairs in scratch memory in global memory
+// (a power of two >= vocab entries per row, padded with -1).  Sums over the sorted prefix are formed per thread
+// over contiguous chunks and combined in chunk order; every sum has a fixed order, so a row's token depends on
+// nothing but its inputs.
 #include "common.cuh"
 
 namespace {
 
 constexpr int THREADS = 1024;
+constexpr int LEVELS = 10;              // coarse thresholds 2^-4, 2^-8, ... 2^-40 of the best probability
+constexpr int BINS = 8;                 // bins of a refinement pass
+constexpr int CANDIDATES = 16384;       // most candidates sorted in shared memory (128 KB)
 
 __global__ void penalty_kernel(const float* __restrict__ src, float* __restrict__ dst, long long row_stride,
                                const int* __restrict__ history, const int* __restrict__ history_start,
@@ -40,28 +51,100 @@ __device__ __forceinline__ bool before(float pa, int ia, float pb, int ib) {
   return pa > pb || (pa == pb && ia < ib);
 }
 
-__global__ void __launch_bounds__(THREADS) sample_cuts_kernel(
+// A probability is at most 1, so its bit pattern orders like its value.  exponents_below(pr) = d with pr in
+// [2^-d, 2^(1-d)); the coarse level of d is 0 for d <= 4, 1 for d <= 8, ...
+__device__ __forceinline__ int exponents_below(float pr) { return 127 - (int)((__float_as_uint(pr) >> 23) & 255u); }
+__device__ __forceinline__ int level_of_exponent(int d) { return d <= 0 ? 0 : (d - 1) / 4; }
+
+// Calls visit(value, index) for every element of data[0, n), each thread of the block taking every 1024th group of
+// four (16-byte loads when the row starts on a 16-byte boundary, which keeps four times as many bytes in flight).
+template <typename Visit>
+__device__ __forceinline__ void for_each_element(const float* __restrict__ data, int n, Visit visit) {
+  const int tid = threadIdx.x;
+  if ((reinterpret_cast<uintptr_t>(data) & 15u) == 0) {
+    const int quads = n >> 2;
+#pragma unroll 4
+    for (int q = tid; q < quads; q += THREADS) {
+      const float4 v = reinterpret_cast<const float4*>(data)[q];
+      visit(v.x, 4 * q);
+      visit(v.y, 4 * q + 1);
+      visit(v.z, 4 * q + 2);
+      visit(v.w, 4 * q + 3);
+    }
+    for (int i = 4 * quads + tid; i < n; i += THREADS) visit(data[i], i);
+  } else {
+#pragma unroll 8
+    for (int i = tid; i < n; i += THREADS) visit(data[i], i);
+  }
+}
+
+// What the walk needs of the candidates above a threshold: enough of them for the top-k, or enough mass for the
+// nucleus's share of the total (with a hair to spare: the sums here and in the walk are formed in different orders).
+struct Need {
+  int k_wanted;          // 0: no top-k
+  float share;           // top-p (>= 1: none)
+  float kept_mass;       // of everything min-p keeps
+  int kept_count;
+  __device__ bool met(int count, float mass) const {
+    if (count == kept_count) return true;                  // everything that is kept at all
+    if (k_wanted > 0) return count >= k_wanted;
+    return share < 1.0f && mass >= share * kept_mass * 1.00001f;
+  }
+};
+
+// Block-wide sums of BINS (or LEVELS + 1) counts and masses in a fixed order: a butterfly in each warp, then the
+// warps in warp order.  Results land in row 0 of the two arrays.
+template <int N>
+__device__ __forceinline__ void block_sums(float (&mass)[N], int (&count)[N], float (*red_mass)[LEVELS + 1],
+                                           int (*red_count)[LEVELS + 1]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __syncthreads();                                   // earlier readers of the arrays are done
+#pragma unroll
+  for (int l = 0; l < N; ++l) {
+    mass[l] = warp_sum(mass[l]);
+    count[l] = __reduce_add_sync(0xffffffffu, count[l]);
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int l = 0; l < N; ++l) { red_mass[warp][l] = mass[l]; red_count[warp][l] = count[l]; }
+  }
+  __syncthreads();
+  if (tid < N) {
+    float m = 0.0f;
+    int c = 0;
+    for (int w = 0; w < THREADS / 32; ++w) { m += red_mass[w][tid]; c += red_count[w][tid]; }
+    red_mass[0][tid] = m;                            // thread t touches only column t
+    red_count[0][tid] = c;
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(THREADS, 1) sample_cuts_kernel(
     const float* __restrict__ scores, long long row_stride, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const float* __restrict__ uniform, float* __restrict__ sort_prob, int* __restrict__ sort_index, int padded,
     int* __restrict__ out, int vocab) {
+  extern __shared__ float few_prob[];                 // [CANDIDATES], then int few_index[CANDIDATES]
+  int* few_index = reinterpret_cast<int*>(few_prob + CANDIDATES);
   __shared__ float red_value[32];
   __shared__ int red_index[32];
   __shared__ float chunk_sum[THREADS];
+  __shared__ float group_sum[32];
   __shared__ float shared_f[4];
-  __shared__ int shared_i[4];
+  __shared__ int shared_i[8];
+  __shared__ float red_mass[THREADS / 32][LEVELS + 1];
+  __shared__ int red_count[THREADS / 32][LEVELS + 1];
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* z = scores + (size_t)row * row_stride;
-  float* prob = sort_prob + (size_t)row * padded;
-  int* index = sort_index + (size_t)row * padded;
+  float* prob = sort_prob + (size_t)row * padded;     // (prob, index and padded move to shared memory below
+  int* index = sort_index + (size_t)row * padded;     //  when few candidates suffice)
 
   // maximum (first index on ties), as in the plain kernel
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < vocab; i += THREADS) {
-    const float v = z[i];
+  for_each_element(z, vocab, [&](float v, int i) {          // (a thread meets its elements in ascending order)
     if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
-  }
+  });
   for (int offset = 16; offset > 0; offset >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, offset);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, offset);
@@ -87,11 +170,159 @@ __global__ void __launch_bounds__(THREADS) sample_cuts_kernel(
     return;
   }
   const float inverse = 1.0f / temp;
-  for (int i = tid; i < padded; i += THREADS) {
-    prob[i] = i < vocab ? expf((z[i] - maximum) * inverse) : -1.0f;
-    index[i] = i;
+  const float floor_value = min_p[row] > 0.0f ? min_p[row] : -1.0f;      // times the best probability, which is exp(0) = 1
+  Need need;
+  need.k_wanted = top_k[row] > 0 ? min(top_k[row], vocab) : 0;
+  need.share = top_p[row];
+
+  // ---- pass 1: probabilities; counts and masses of the coarse levels and of everything min-p keeps ----
+  {
+    float mass[LEVELS + 1];
+    int count[LEVELS + 1];
+#pragma unroll
+    for (int l = 0; l <= LEVELS; ++l) { mass[l] = 0.0f; count[l] = 0; }
+    float* const prob_out = prob;
+    for_each_element(z, vocab, [&](float v, int i) {
+      const float pr = expf((v - maximum) * inverse);
+      prob_out[i] = pr;
+      const bool kept = pr >= floor_value;
+      const int level = kept ? level_of_exponent(exponents_below(pr)) : -1;
+      mass[LEVELS] += kept ? pr : 0.0f;
+      count[LEVELS] += kept ? 1 : 0;
+#pragma unroll
+      for (int l = 0; l < LEVELS; ++l) {
+        mass[l] += level == l ? pr : 0.0f;
+        count[l] += level == l ? 1 : 0;
+      }
+    });
+    block_sums<LEVELS + 1>(mass, count, red_mass, red_count);
+  }
+  need.kept_mass = red_mass[0][LEVELS];
+  need.kept_count = red_count[0][LEVELS];
+  // Thread 0 narrows the threshold; everybody follows through shared_i:
+  //   [1] state: 0 searching, 1 found, -1 the full sort   [2] exponent range top   [3] candidates so far
+  //   [4] threshold bits (found)   shared_f[2]: mass so far
+  if (tid == 0) {
+    int state = -1, running_count = 0, level = 0;
+    float running_mass = 0.0f;
+    if (need.kept_count <= CANDIDATES) {             // all that is kept fits: no threshold beyond the floor
+      state = 1;
+      shared_i[4] = 0;
+    } else {
+      for (; level < LEVELS; ++level) {
+        if (need.met(running_count + red_count[0][level], running_mass + red_mass[0][level])) { state = 0; break; }
+        running_count += red_count[0][level];
+        running_mass += red_mass[0][level];
+      }
+      if (running_count > CANDIDATES) state = -1;
+    }
+    shared_i[1] = state;
+    shared_i[2] = level;
+    shared_i[3] = running_count;
+    shared_f[2] = running_mass;
   }
   __syncthreads();
+  if (shared_i[1] == 0) {
+    // ---- pass 2: the four exponents of the chosen coarse level (bins 0..3; level 0 also holds exponent 0) ----
+    const int level = shared_i[2];
+    // bin = d - (4 level + 1); the one probability with d = 0 (the best: exactly 1) goes with d = 1
+    float mass[BINS];
+    int count[BINS];
+#pragma unroll
+    for (int l = 0; l < BINS; ++l) { mass[l] = 0.0f; count[l] = 0; }
+    for_each_element(prob, vocab, [&](float pr, int) {
+      const int d = exponents_below(pr);
+      const bool inside = pr >= floor_value && level_of_exponent(d) == level;
+      const int bin = inside ? max(d - (4 * level + 1), 0) : -1;
+#pragma unroll
+      for (int l = 0; l < 4; ++l) {
+        mass[l] += bin == l ? pr : 0.0f;
+        count[l] += bin == l ? 1 : 0;
+      }
+    });
+    block_sums<BINS>(mass, count, red_mass, red_count);
+    if (tid == 0) {
+      int running_count = shared_i[3], bin = 0;
+      float running_mass = shared_f[2];
+      for (; bin < 3; ++bin) {
+        if (need.met(running_count + red_count[0][bin], running_mass + red_mass[0][bin])) break;
+        running_count += red_count[0][bin];
+        running_mass += red_mass[0][bin];
+      }
+      shared_i[2] = 4 * level + 1 + bin;                               // the exponent d (>= 1) in which the threshold lies
+      shared_i[3] = running_count;
+      shared_f[2] = running_mass;
+      if (running_count > CANDIDATES) shared_i[1] = -1;
+    }
+    __syncthreads();
+  }
+  if (shared_i[1] == 0) {
+    // ---- pass 3: eight bins of the mantissa within that exponent, highest first ----
+    const int d_in = shared_i[2];
+    float mass[BINS];
+    int count[BINS];
+#pragma unroll
+    for (int l = 0; l < BINS; ++l) { mass[l] = 0.0f; count[l] = 0; }
+    for_each_element(prob, vocab, [&](float pr, int) {
+      const int d = exponents_below(pr);
+      const bool inside = pr >= floor_value && max(d, 1) == d_in;
+      const int bin = !inside ? -1 : (d <= 0 ? 0 : 7 - (int)((__float_as_uint(pr) >> 20) & 7u));
+#pragma unroll
+      for (int l = 0; l < BINS; ++l) {
+        mass[l] += bin == l ? pr : 0.0f;
+        count[l] += bin == l ? 1 : 0;
+      }
+    });
+    block_sums<BINS>(mass, count, red_mass, red_count);
+    if (tid == 0) {
+      int running_count = shared_i[3], bin = 0;
+      float running_mass = shared_f[2];
+      for (; bin < BINS - 1; ++bin) {
+        if (need.met(running_count + red_count[0][bin], running_mass + red_mass[0][bin])) break;
+        running_count += red_count[0][bin];
+        running_mass += red_mass[0][bin];
+      }
+      running_count += red_count[0][bin];
+      // candidates: every kept probability whose bits reach those of the chosen bin's lower edge
+      const unsigned int exponent_field = (unsigned int)max(127 - d_in, 0);
+      shared_i[4] = (int)((exponent_field << 23) | ((unsigned int)(7 - bin) << 20));
+      shared_i[1] = running_count <= CANDIDATES ? 1 : -1;
+    }
+    __syncthreads();
+  }
+  const bool few = shared_i[1] == 1;
+  const float kept_total = need.kept_mass;
+  int count_here = vocab;               // entries of the sorted arrays that are real
+  if (few) {
+    // ---- gather the candidates into shared memory and sort them there ----
+    const unsigned int threshold_bits = (unsigned int)shared_i[4];
+    if (tid == 0) shared_i[5] = 0;
+    __syncthreads();
+    for_each_element(prob, vocab, [&](float pr, int i) {
+      if (pr >= floor_value && __float_as_uint(pr) >= threshold_bits) {
+        const int slot = atomicAdd(&shared_i[5], 1);
+        if (slot < CANDIDATES) {
+          few_prob[slot] = pr;
+          few_index[slot] = i;
+        }
+      }
+    });
+    __syncthreads();
+    count_here = min(shared_i[5], CANDIDATES);
+    int padded_few = 2;
+    while (padded_few < count_here) padded_few <<= 1;
+    for (int i = count_here + tid; i < padded_few; i += THREADS) { few_prob[i] = -1.0f; few_index[i] = 0x7fffffff; }
+    __syncthreads();
+    prob = few_prob;
+    index = few_index;
+    padded = padded_few;
+  } else {
+    for (int i = tid; i < padded; i += THREADS) {
+      if (i >= vocab) prob[i] = -1.0f;
+      index[i] = i;
+    }
+    __syncthreads();
+  }
 
   // bitonic sort, descending by (probability, -index)
   for (int size = 2; size <= padded; size <<= 1) {
@@ -113,8 +344,7 @@ __global__ void __launch_bounds__(THREADS) sample_cuts_kernel(
   }
 
   // how many candidates survive top-k and min-p (a prefix of the sorted order)
-  int keep = top_k[row] > 0 ? min(top_k[row], vocab) : vocab;
-  const float floor_value = min_p[row] > 0.0f ? min_p[row] * prob[0] : -1.0f;
+  int keep = need.k_wanted > 0 ? min(need.k_wanted, count_here) : count_here;
   if (tid == 0) shared_i[1] = keep;
   __syncthreads();
   if (min_p[row] > 0.0f) {
@@ -128,33 +358,54 @@ __global__ void __launch_bounds__(THREADS) sample_cuts_kernel(
     if (tid == 0) out[row] = index[0];
     return;
   }
+  // Without a top-k the total is the mass of everything min-p keeps, which the candidates need not all be:
+  // it was summed in the first pass.
+  const bool total_known = few && need.k_wanted == 0;
 
-  // chunked prefix sums over the kept prefix, in chunk order
+  // Sums over the kept prefix in a fixed order: every thread adds a contiguous chunk, 32 threads add 32 chunk sums
+  // each (a group), one thread adds the 32 group sums; the walks below skip whole groups and chunks the same way.
+  constexpr int GROUP = 32;
   const int chunk = (keep + THREADS - 1) / THREADS;
   const int begin = min(tid * chunk, keep), end = min(begin + chunk, keep);
   float local = 0.0f;
   for (int i = begin; i < end; ++i) local += prob[i];
   chunk_sum[tid] = local;
   __syncthreads();
+  if (tid < GROUP) {
+    float sum = 0.0f;
+    for (int c = 0; c < THREADS / GROUP; ++c) sum += chunk_sum[tid * (THREADS / GROUP) + c];
+    group_sum[tid] = sum;
+  }
+  __syncthreads();
   if (tid == 0) {
     float total = 0.0f;
-    for (int c = 0; c < THREADS; ++c) total += chunk_sum[c];
+    for (int g = 0; g < GROUP; ++g) total += group_sum[g];
+    if (total_known) total = kept_total;
     shared_f[1] = total;
     // nucleus: shortest prefix whose share of the total reaches top_p
     int limit = keep;
-    const float nucleus = top_p[row];
+    const float nucleus = need.share;
     if (nucleus < 1.0f && total > 0.0f) {
       float cumulative = 0.0f;
       bool found = false;
-      for (int c = 0; c < THREADS && !found; ++c) {
-        const int cb = min(c * chunk, keep), ce = min(cb + chunk, keep);
-        if ((cumulative + chunk_sum[c]) / total < nucleus && c + 1 < THREADS && ce < keep) {
-          cumulative += chunk_sum[c];
+      for (int g = 0; g < GROUP && !found; ++g) {
+        const int first_chunk = g * (THREADS / GROUP);
+        if (first_chunk * chunk >= keep) break;
+        if ((cumulative + group_sum[g]) / total < nucleus && (first_chunk + THREADS / GROUP) * chunk < keep) {
+          cumulative += group_sum[g];
           continue;
         }
-        for (int i = cb; i < ce; ++i) {
-          cumulative += prob[i];
-          if (cumulative / total >= nucleus) { limit = i + 1; found = true; break; }
+        for (int c = first_chunk; c < first_chunk + THREADS / GROUP && !found; ++c) {
+          const int cb = min(c * chunk, keep), ce = min(cb + chunk, keep);
+          if (cb >= ce) break;
+          if ((cumulative + chunk_sum[c]) / total < nucleus && ce < keep) {
+            cumulative += chunk_sum[c];
+            continue;
+          }
+          for (int i = cb; i < ce; ++i) {
+            cumulative += prob[i];
+            if (cumulative / total >= nucleus) { limit = i + 1; found = true; break; }
+          }
         }
       }
     }
@@ -175,23 +426,34 @@ __global__ void __launch_bounds__(THREADS) sample_cuts_kernel(
   __syncthreads();
   chunk_sum[tid] = local;
   __syncthreads();
+  if (tid < GROUP) {
+    float sum = 0.0f;
+    for (int c = 0; c < THREADS / GROUP; ++c) sum += chunk_sum[tid * (THREADS / GROUP) + c];
+    group_sum[tid] = sum;
+  }
+  __syncthreads();
   if (tid == 0) {
     float kept = 0.0f;
-    for (int c = 0; c < THREADS; ++c) kept += chunk_sum[c];
+    for (int g = 0; g < GROUP; ++g) kept += group_sum[g];
     int result = index[0];
     if (kept > 0.0f) {
       float target = uniform[row] * kept;
       result = index[limit - 1];
       bool found = false;
-      for (int c = 0; c < THREADS && !found; ++c) {
-        const int cb = min(c * chunk2, limit), ce = min(cb + chunk2, limit);
-        if (cb >= ce) break;
-        if (target - chunk_sum[c] > 0.0f) { target -= chunk_sum[c]; continue; }
-        for (int i = cb; i < ce; ++i) {
-          target -= prob[i];
-          if (target <= 0.0f) { result = index[i]; found = true; break; }
+      for (int g = 0; g < GROUP && !found; ++g) {
+        const int first_chunk = g * (THREADS / GROUP);
+        if (first_chunk * chunk2 >= limit) break;
+        if (target - group_sum[g] > 0.0f) { target -= group_sum[g]; continue; }
+        for (int c = first_chunk; c < first_chunk + THREADS / GROUP && !found; ++c) {
+          const int cb = min(c * chunk2, limit), ce = min(cb + chunk2, limit);
+          if (cb >= ce) break;
+          if (target - chunk_sum[c] > 0.0f) { target -= chunk_sum[c]; continue; }
+          for (int i = cb; i < ce; ++i) {
+            target -= prob[i];
+            if (target <= 0.0f) { result = index[i]; found = true; break; }
+          }
+          if (!found) { result = index[ce - 1]; found = true; }
         }
-        if (!found) { result = index[ce - 1]; found = true; }
       }
     }
     out[row] = result;
@@ -224,8 +486,18 @@ TGE_API int tge_sample_cuts(const float* scores, long long row_stride, const flo
   TGE_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample_cuts: bad sizes rows=%d vocab=%d", rows, vocab);
   TGE_REQUIRE(sort_prob != nullptr && sort_index != nullptr, "sample_cuts: needs scratch for the sort");
   if (rows == 0) return 0;
-  sample_cuts_kernel<<<rows, THREADS, 0, stream>>>(scores, row_stride, temperature, top_k, top_p, min_p, uniform,
-                                                   sort_prob, sort_index, (int)tge_sample_cuts_padded(vocab), out,
-                                                   vocab);
+  const size_t smem = (size_t)CANDIDATES * (sizeof(float) + sizeof(int));
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(sample_cuts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) {
+      tge_set_error("sample_cuts: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+      return -2;
+    }
+    configured = true;
+  }
+  sample_cuts_kernel<<<rows, THREADS, smem, stream>>>(scores, row_stride, temperature, top_k, top_p, min_p, uniform,
+                                                      sort_prob, sort_index, (int)tge_sample_cuts_padded(vocab), out,
+                                                      vocab);
   return tge_launched("sample_cuts", 1);
 }

@@ -99,15 +99,15 @@ class ClockSampler:
         return {"sm_mhz": median, "sm_max_mhz": peak, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def end_to_end(engine, batch, steps, warmup):
-    """Decode steps through the public entry point: host token ids in, sampled ids out, every step.
-    Returns (tokens per second, host-to-device bytes per step, device-to-host bytes per step)."""
+def end_to_end(engine, batch, steps, warmup, sampling=None):
+    """Decode steps through the public entry point: host token ids in, sampled ids out, every step (greedy, or
+    with ``sampling``).  Returns (tokens per second, host-to-device bytes per step, device-to-host bytes per step)."""
     import time
     import torch
     from aegean_tge_b200.bench_tools import _random_tokens
     vocab = engine.spec.vocab_size
     for b in range(batch):
-        engine.add_request(_random_tokens(vocab, PROMPT, seed=2000 + b), n=warmup + steps + batch + 4)
+        engine.add_request(_random_tokens(vocab, PROMPT, seed=2000 + b), n=warmup + steps + batch + 4, sampling=sampling)
     while any(not r.output for r in engine.scheduler.running) or engine.scheduler.waiting:
         engine.step()                                   # prefill and the first token, untimed
     for _ in range(warmup):
@@ -209,6 +209,8 @@ def main() -> int:
                 points[f"decode_b{batch}_hbm_frac"] = rnd(run["frac"], 4)
                 points[f"e2e_b{batch}"] = rnd(end_to_end(engine, batch, short, args.warmup)[0])
             points["mixed_step_ms"] = rnd(bench_mixed(engine, 63, PROMPT, PROMPT - 63)["ms"], 3)
+            cuts = tge.SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1)     # what the cuts cost a step
+            points["e2e_b8_top_k50_top_p"] = rnd(end_to_end(engine, BATCH, short, args.warmup, sampling=cuts)[0])
         group("batches", other_batches)
         del engine
 

@@ -62,6 +62,44 @@ def test_cuts_pick_what_the_plain_sampler_picks(ops, vocab, top_k, top_p, min_p)
             assert between < vocab * 2.0 ** -23, (r, ids[r], expected, between)
 
 
+@pytest.mark.parametrize("spread,top_k,top_p,min_p", [(4.0, 0, 0.9, 0.0), (4.0, 50, 0.95, 0.0), (4.0, 0, 1.0, 0.001),
+                                                     (0.3, 0, 0.9, 0.0), (0.3, 6000, 0.5, 0.0), (0.0, 0, 0.5, 0.0)])
+def test_cuts_at_a_real_vocabulary(ops, spread, top_k, top_p, min_p):
+    """152,064 scores per row.  Peaked rows (a spread of 4) are settled among a few thousand candidates sorted in
+    shared memory; flat rows (0.3: the nucleus is most of the vocabulary; 0: all scores equal, every probability
+    ties and the lower index goes first) and a top-k beyond the candidates take the full sort.  Both give the
+    plain sampler's token, up to the rounding of the sums."""
+    vocab, rows = 152064, 3
+    gen = torch.Generator().manual_seed(int(spread * 10) + top_k)
+    logits = torch.randn(rows, vocab, generator=gen) * spread
+    temps, uniforms = [0.8, 1.0, 1.3], [0.37, 0.93, 0.05]
+    mk = lambda v, dt: torch.tensor(v, dtype=dt, device=DEV)
+    args = (mk(temps, torch.float32), mk([top_k] * rows, torch.int32), mk([top_p] * rows, torch.float32),
+            mk([min_p] * rows, torch.float32), mk(uniforms, torch.float32))
+    ids = ops.sample_cuts(logits.to(DEV), *args).cpu().tolist()
+    assert ids == ops.sample_cuts(logits.to(DEV), *args).cpu().tolist()          # the same token every time
+    for r in range(rows):
+        z = logits[r].double()
+        prob = torch.exp((z - z.max()) / temps[r])
+        order = torch.tensor(sorted(range(vocab), key=lambda i: (-float(prob[i]), i)))
+        # the plain walk in float64 over the sorted order (the float32 walk is the same up to the rounding let through below)
+        keep = min(top_k, vocab) if top_k > 0 else vocab
+        kept = order[:keep]
+        if min_p > 0.0:
+            kept = kept[prob[kept] >= min_p * prob[kept[0]]]
+        mass = torch.cumsum(prob[kept], 0)
+        limit = len(kept)
+        if top_p < 1.0:
+            limit = int(torch.searchsorted(mass / mass[-1], torch.tensor(top_p, dtype=torch.float64))) + 1
+        target = uniforms[r] * float(mass[limit - 1])
+        expected_position = min(int(torch.searchsorted(mass[:limit], torch.tensor(target, dtype=torch.float64))), limit - 1)
+        position = int((kept == ids[r]).nonzero()[0]) if ids[r] in kept.tolist() else -1
+        assert position >= 0, (r, ids[r])
+        a, b = sorted((position, expected_position))
+        between = float(prob[kept[a:b]].sum()) / float(mass[-1])
+        assert between < vocab * 2.0 ** -23, (r, position, expected_position, between)
+
+
 def test_cut_draws_stay_inside_the_cut_and_follow_the_distribution(ops):
     """Many draws with top-k 3 from a known distribution: nothing outside the top three, shares as renormalised."""
     from aegean_tge_b200.sampling import XorShift32
