@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(THREADS, 1) sample_cuts_kernel(
     const float* __restrict__ scores, long long row_stride, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
     const float* __restrict__ uniform, float* __restrict__ sort_prob, int* __restrict__ sort_index, int padded,
-    int* __restrict__ out, int vocab) {
+    int* __restrict__ out, int vocab, int skip_uncut) {
+  // a row with every cut switched off keeps the id it was given (the kernel without cuts drew it)
+  if (skip_uncut && !(top_k[blockIdx.x] > 0 || top_p[blockIdx.x] < 1.0f || min_p[blockIdx.x] > 0.0f)) return;
   extern __shared__ float few_prob[];                 // [CANDIDATES], then int few_index[CANDIDATES]
   int* few_index = reinterpret_cast<int*>(few_prob + CANDIDATES);
   __shared__ float red_value[32];
@@ -480,9 +482,10 @@ TGE_API long long tge_sample_cuts_padded(int vocab) {
 }
 
 // scratch: sort_prob float32 [rows, padded], sort_index int32 [rows, padded] with padded from tge_sample_cuts_padded.
+// skip_uncut: rows whose cuts are all switched off (top_k 0, top_p >= 1, min_p <= 0) are left untouched in `out`.
 TGE_API int tge_sample_cuts(const float* scores, long long row_stride, const float* temperature, const int* top_k,
                             const float* top_p, const float* min_p, const float* uniform, float* sort_prob,
-                            int* sort_index, int* out, int rows, int vocab, cudaStream_t stream) {
+                            int* sort_index, int* out, int rows, int vocab, int skip_uncut, cudaStream_t stream) {
   TGE_REQUIRE(rows >= 0 && vocab > 0 && row_stride >= vocab, "sample_cuts: bad sizes rows=%d vocab=%d", rows, vocab);
   TGE_REQUIRE(sort_prob != nullptr && sort_index != nullptr, "sample_cuts: needs scratch for the sort");
   if (rows == 0) return 0;
@@ -498,6 +501,6 @@ TGE_API int tge_sample_cuts(const float* scores, long long row_stride, const flo
   }
   sample_cuts_kernel<<<rows, THREADS, smem, stream>>>(scores, row_stride, temperature, top_k, top_p, min_p, uniform,
                                                       sort_prob, sort_index, (int)tge_sample_cuts_padded(vocab), out,
-                                                      vocab);
+                                                      vocab, skip_uncut);
   return tge_launched("sample_cuts", 1);
 }

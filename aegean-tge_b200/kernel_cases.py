@@ -4,6 +4,7 @@
     python -m aegean_tge_b200.kernel_cases attention --batch 64 --context 2048 --q-len 1
     python -m aegean_tge_b200.kernel_cases attention --batch 1 --context 2048 --q-len 2048
     python -m aegean_tge_b200.kernel_cases fill --elements 545000000
+    python -m aegean_tge_b200.kernel_cases sample --rows 8 --top-k 50 --top-p 0.9
 
 Weights are rotated between launches so that a launch never finds them in L2; attention reads a
 freshly shuffled page table.  Sizes default to the Qwen2.5-7B layer shapes.
@@ -93,6 +94,32 @@ def run_fill(args) -> None:
     print(f"fill {args.elements} bfloat16 elements: {us:.1f} us, written at {args.elements * 2 / us / 1e3:.0f} GB/s")
 
 
+def run_sample(args) -> None:
+    """The sampling kernels on rows of scores as peaked as a language model's (a normal spread of ``--spread``)."""
+    dev = "cuda:0"
+    gen = torch.Generator(device=dev).manual_seed(3)
+    scores = torch.randn(args.rows, args.vocab, generator=gen, device=dev) * args.spread
+    temperature = torch.full((args.rows,), 0.8, device=dev)
+    uniform = torch.rand(args.rows, generator=gen, device=dev)
+    top_k = torch.full((args.rows,), args.top_k, dtype=torch.int32, device=dev)
+    top_p = torch.full((args.rows,), args.top_p, device=dev)
+    min_p = torch.full((args.rows,), args.min_p, device=dev)
+    cuts = args.top_k > 0 or args.top_p < 1.0 or args.min_p > 0.0
+    run = (lambda: ops.sample_cuts(scores, temperature, top_k, top_p, min_p, uniform)) if cuts else \
+          (lambda: ops.sample(scores, temperature, uniform))
+    for _ in range(3):
+        run()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(args.repeat):
+        run()
+    stop.record()
+    torch.cuda.synchronize()
+    print(f"sample rows={args.rows} vocab={args.vocab} top_k={args.top_k} top_p={args.top_p} min_p={args.min_p}: "
+          f"{start.elapsed_time(stop) * 1e3 / args.repeat:.1f} us per call (with the host's launch cost)")
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="kernel_cases", description=__doc__.split("\n\n")[0])
     sub = parser.add_subparsers(dest="what", required=True)
@@ -117,11 +144,21 @@ def main(argv=None) -> int:
     fill = sub.add_parser("fill")
     fill.add_argument("--elements", type=int, default=152064 * 3584)
     fill.add_argument("--repeat", type=int, default=5)
+    sample = sub.add_parser("sample")
+    sample.add_argument("--rows", type=int, default=8)
+    sample.add_argument("--vocab", type=int, default=152064)
+    sample.add_argument("--spread", type=float, default=3.0)
+    sample.add_argument("--top-k", type=int, default=0)
+    sample.add_argument("--top-p", type=float, default=1.0)
+    sample.add_argument("--min-p", type=float, default=0.0)
+    sample.add_argument("--repeat", type=int, default=10)
     args = parser.parse_args(argv)
     if args.what == "gemm":
         run_gemm(args)
     elif args.what == "fill":
         run_fill(args)
+    elif args.what == "sample":
+        run_sample(args)
     else:
         run_attention(args)
     ops.check_status()

@@ -91,7 +91,7 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_sample", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_apply_penalty", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_sample_cuts", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                                          _c_int, _c_int, _c_ptr])
+                                          _c_int, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_random_fill", [_c_ptr, _c_int, _c_ll, _c_ll, ctypes.c_ulonglong, _c_int, _c_float, _c_int,
                                           ctypes.c_uint, _c_ptr])
         _declare(lib, "tge_wait_gives_up", [_c_ptr, _c_ll, _c_ptr, _c_ptr])
@@ -660,8 +660,9 @@ def apply_penalty(logits: torch.Tensor, history: torch.Tensor, history_start: to
 
 
 def sample_cuts(scores: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-                min_p: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
-    """One token per row with the top-k / min-p / top-p cuts (0 / 0.0 / 1.0 switch a cut off)."""
+                min_p: torch.Tensor, uniform: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row with the top-k / min-p / top-p cuts (0 / 0.0 / 1.0 switch a cut off).  Given ``out``
+    (int32 [rows], already holding ids), rows with every cut switched off are left as they are."""
     _want(scores, "scores", torch.float32, contiguous=False)
     stride = _rows_2d(scores, "scores")
     rows, vocab = scores.shape
@@ -675,8 +676,13 @@ def sample_cuts(scores: torch.Tensor, temperature: torch.Tensor, top_k: torch.Te
     padded = lib.tge_sample_cuts_padded(vocab)
     sort_prob = torch.empty((rows, padded), dtype=torch.float32, device=scores.device)
     sort_index = torch.empty((rows, padded), dtype=torch.int32, device=scores.device)
-    out = torch.empty(rows, dtype=torch.int32, device=scores.device)
+    skip_uncut = out is not None
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=scores.device)
+    _want(out, "sampled ids", torch.int32)
+    if out.numel() != rows:
+        raise KernelError("sample_cuts: one id per row")
     _check(lib.tge_sample_cuts(scores.data_ptr(), stride, temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(),
                                min_p.data_ptr(), uniform.data_ptr(), sort_prob.data_ptr(), sort_index.data_ptr(),
-                               out.data_ptr(), rows, vocab, _stream()), lib)
+                               out.data_ptr(), rows, vocab, int(skip_uncut), _stream()), lib)
     return out

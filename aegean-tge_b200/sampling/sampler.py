@@ -34,22 +34,37 @@ class Sampler:
 
     @staticmethod
     def stays_on_device(params: Sequence[SamplingParams]) -> bool:
-        """True when every row is greedy or a plain temperature draw: no history, no sort, one kernel."""
-        return all(not p.has_penalty and (p.greedy or not p.has_cuts) for p in params)
+        """True when no row needs its token history (the repetition penalty): greedy rows, temperature draws and
+        the top-k / top-p / min-p cuts are all settled by kernels that read only what is on the device."""
+        return all(not p.has_penalty for p in params)
+
+    def _draw(self, scores: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[XorShift32]) -> torch.Tensor:
+        """Token ids on the device for rows of scores: one kernel for all rows, one more for the rows with cuts."""
+        rows = scores.shape[0]
+        if all(p.greedy for p in params):
+            if rows not in self._zeros:
+                self._zeros[rows] = torch.zeros((2, rows), dtype=torch.float32, device=self.device)
+            floats = self._zeros[rows]
+            return self.ops.sample(scores, floats[0], floats[1])
+        cuts = any(p.has_cuts and not p.greedy for p in params)
+        table = [[max(float(p.temperature), 0.0) for p in params],
+                 [0.0 if p.greedy else rng.next_uniform() for p, rng in zip(params, rngs)]]
+        if cuts:
+            off = lambda p: p.greedy or not p.has_cuts
+            table.append([1.0 if off(p) else float(p.top_p) for p in params])
+            table.append([0.0 if off(p) else float(p.min_p) for p in params])
+        floats = self._to_device(table, torch.float32)
+        ids = self.ops.sample(scores, floats[0], floats[1])
+        if cuts:
+            top_k = self._to_device([0 if p.greedy or not p.has_cuts else int(p.top_k) for p in params], torch.int32)
+            self.ops.sample_cuts(scores, floats[0], top_k, floats[2], floats[3], floats[1], out=ids)
+        return ids
 
     def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], rngs: Sequence[XorShift32]):
         """Like :meth:`sample` for rows that stay on the device, without waiting: returns the ids on the
         device, their copy in pinned host memory, and the event after which that copy is complete."""
         rows = logits.shape[0]
-        if all(p.greedy for p in params):
-            if rows not in self._zeros:
-                self._zeros[rows] = torch.zeros((2, rows), dtype=torch.float32, device=self.device)
-            floats = self._zeros[rows]
-        else:
-            floats = self._to_device([[max(float(p.temperature), 0.0) for p in params],
-                                      [0.0 if p.greedy else rng.next_uniform() for p, rng in zip(params, rngs)]],
-                                     torch.float32)
-        ids = self.ops.sample(logits, floats[0], floats[1])
+        ids = self._draw(logits, params, rngs)
         turn = self._turn = (getattr(self, "_turn", -1) + 1) % 4
         if rows not in self._pinned:
             self._pinned[rows] = [torch.empty(rows, dtype=torch.int32).pin_memory() for _ in range(4)]
@@ -68,11 +83,8 @@ class Sampler:
         rows = logits.shape[0]
         if rows != len(params) or rows != len(rngs):
             raise ValueError("sampler: one SamplingParams and one generator per logits row")
-        temperatures, uniforms = [], []
-        for p, rng in zip(params, rngs):
+        for p in params:
             p.validate()
-            temperatures.append(max(float(p.temperature), 0.0))
-            uniforms.append(0.0 if p.greedy else rng.next_uniform())
         scores = logits
         if any(p.has_penalty for p in params):
             if histories is None:
@@ -87,22 +99,4 @@ class Sampler:
             scores = self.ops.apply_penalty(logits, self._to_device(flat or [0], torch.int32),
                                             self._to_device(starts, torch.int32),
                                             self._to_device([float(p.repeat_penalty) for p in params], torch.float32))
-        if all(p.greedy for p in params):
-            if rows not in self._zeros:
-                self._zeros[rows] = torch.zeros((2, rows), dtype=torch.float32, device=self.device)
-            floats = self._zeros[rows]
-        else:
-            floats = self._to_device([temperatures, uniforms], torch.float32)
-        cut_rows = [i for i, p in enumerate(params) if p.has_cuts and not p.greedy]
-        if not cut_rows:
-            return self.ops.sample(scores, floats[0], floats[1]).cpu().tolist()
-        ids = self.ops.sample(scores, floats[0], floats[1])
-        picked = self._to_device(cut_rows, torch.int64)
-        cut_ids = self.ops.sample_cuts(
-            scores.index_select(0, picked), floats[0].index_select(0, picked),
-            self._to_device([params[i].top_k for i in cut_rows], torch.int32),
-            self._to_device([params[i].top_p for i in cut_rows], torch.float32),
-            self._to_device([params[i].min_p for i in cut_rows], torch.float32),
-            floats[1].index_select(0, picked))
-        ids[picked] = cut_ids
-        return ids.cpu().tolist()
+        return self._draw(scores, params, rngs).cpu().tolist()
