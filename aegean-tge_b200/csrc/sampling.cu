@@ -42,9 +42,24 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   // first maximal index
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < vocab; i += 1024) {
-    const float v = z[i];
+  // (a thread meets its indices in ascending order, four at a time where the row allows 16-byte loads)
+  auto visit = [&](float v, int i) {
     if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
+  };
+  if ((reinterpret_cast<uintptr_t>(z) & 15u) == 0) {
+    const int quads = vocab >> 2;
+#pragma unroll 4
+    for (int q = tid; q < quads; q += 1024) {
+      const float4 v = reinterpret_cast<const float4*>(z)[q];
+      visit(v.x, 4 * q);
+      visit(v.y, 4 * q + 1);
+      visit(v.z, 4 * q + 2);
+      visit(v.w, 4 * q + 3);
+    }
+    for (int i = 4 * quads + tid; i < vocab; i += 1024) visit(z[i], i);
+  } else {
+#pragma unroll 8
+    for (int i = tid; i < vocab; i += 1024) visit(z[i], i);
   }
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) {
@@ -77,6 +92,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   const int begin = warp * segment;
   const int end = min(begin + segment, vocab);
   float partial = 0.0f;
+#pragma unroll 8
   for (int i = begin + lane; i < end; i += 32) partial += expf((z[i] - maximum) * inverse);
   partial = warp_sum(partial);
   if (lane == 0) segment_sum[warp] = partial;

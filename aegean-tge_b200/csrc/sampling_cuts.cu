@@ -179,24 +179,33 @@ __global__ void __launch_bounds__(THREADS, 1) sample_cuts_kernel(
 
   // ---- pass 1: probabilities; counts and masses of the coarse levels and of everything min-p keeps ----
   {
-    float mass[LEVELS + 1];
-    int count[LEVELS + 1];
+    // every thread keeps its level sums in a column of its own in the shared memory that later holds the candidates
+    float* const level_mass = few_prob;                                    // [LEVELS][THREADS]
+    int* const level_count = reinterpret_cast<int*>(few_prob + LEVELS * THREADS);
 #pragma unroll
-    for (int l = 0; l <= LEVELS; ++l) { mass[l] = 0.0f; count[l] = 0; }
+    for (int l = 0; l < LEVELS; ++l) { level_mass[l * THREADS + tid] = 0.0f; level_count[l * THREADS + tid] = 0; }
+    float kept_mass = 0.0f;
+    int kept_count = 0;
     float* const prob_out = prob;
     for_each_element(z, vocab, [&](float v, int i) {
       const float pr = expf((v - maximum) * inverse);
       prob_out[i] = pr;
-      const bool kept = pr >= floor_value;
-      const int level = kept ? level_of_exponent(exponents_below(pr)) : -1;
-      mass[LEVELS] += kept ? pr : 0.0f;
-      count[LEVELS] += kept ? 1 : 0;
-#pragma unroll
-      for (int l = 0; l < LEVELS; ++l) {
-        mass[l] += level == l ? pr : 0.0f;
-        count[l] += level == l ? 1 : 0;
+      if (pr >= floor_value) {
+        kept_mass += pr;
+        ++kept_count;
+        const int level = level_of_exponent(exponents_below(pr));
+        if (level < LEVELS) {
+          level_mass[level * THREADS + tid] += pr;
+          level_count[level * THREADS + tid] += 1;
+        }
       }
     });
+    float mass[LEVELS + 1];
+    int count[LEVELS + 1];
+#pragma unroll
+    for (int l = 0; l < LEVELS; ++l) { mass[l] = level_mass[l * THREADS + tid]; count[l] = level_count[l * THREADS + tid]; }
+    mass[LEVELS] = kept_mass;
+    count[LEVELS] = kept_count;
     block_sums<LEVELS + 1>(mass, count, red_mass, red_count);
   }
   need.kept_mass = red_mass[0][LEVELS];
