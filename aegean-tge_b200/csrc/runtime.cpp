@@ -253,7 +253,7 @@ struct PortionView {
 
 int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int vocab_size, int max_model_len,
               int fixed_width, int pad_rows, bool reserve, int* out, long long capacity, TgeRtStepLayout* layout) {
-  const int S = (int)portions.size();
+  int S = (int)portions.size();
   if (S == 0) return fail(TGE_RT_VALUE_ERROR, "step: no portions");
   if ((int)cache->groups.size() > 8) return fail(TGE_RT_VALUE_ERROR, "step: more than 8 cache groups");
   // validate before touching anything
@@ -263,6 +263,8 @@ int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int v
       if (!seen.insert(p.request).second)
         return fail(TGE_RT_VALUE_ERROR, "request %lld appears twice in one step", (long long)p.request);
       if (p.count <= 0) return fail(TGE_RT_VALUE_ERROR, "request %lld: a portion needs at least one token", (long long)p.request);
+      if (p.count > 1 && pad_rows > S)
+        return fail(TGE_RT_VALUE_ERROR, "step: only a step of single tokens can be padded (%d portions to %d)", S, pad_rows);
       for (int i = 0; i < p.count; ++i)
         if (p.tokens[i] < 0 || p.tokens[i] >= vocab_size)
           return fail(TGE_RT_VALUE_ERROR, "request %lld: token %d is outside the vocabulary of %d", (long long)p.request,
@@ -311,6 +313,13 @@ int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int v
     max_q = std::max(max_q, p.count);
     max_ctx = std::max(max_ctx, live->computed + p.count);
   }
+  // A step padded to more portions than it has gets idle ones behind the real ones: one token (id 0) at
+  // position 0 of the group's scratch page, its state in the scratch slot.  They read and write nothing
+  // that a request holds, and nobody asks for their logits.
+  const int idle = std::max(0, pad_rows - S);
+  const int real_tokens = T;
+  S += idle;
+  T += idle;
   const int G = (int)cache->groups.size();
   int cursor = 0;
   auto section = [&](int count) { const int at = cursor; cursor += count; return at; };
@@ -334,7 +343,7 @@ int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int v
   int token = 0, row = 0;
   out[L.q_start] = 0;
   for (int i = R; i < pad_rows; ++i) out[L.logit_rows + i] = 0;
-  for (int s = 0; s < S; ++s) {
+  for (int s = 0; s < S - idle; ++s) {
     const PortionView& p = portions[s];
     const TgeRtCache::Live* live = cache->find(p.request);
     const int start = live->computed;
@@ -357,6 +366,20 @@ int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int v
                     L.width[g]);
       for (int i = 0; i < have; ++i) dst[i] = it->second[i];
       for (int i = have; i < L.width[g]; ++i) dst[i] = NO_PAGE;
+    }
+  }
+  for (int s = S - idle, token = real_tokens; s < S; ++s, ++token) {
+    out[L.token_ids + token] = 0;
+    out[L.positions + token] = 0;
+    out[L.seq_of_token + token] = s;
+    out[L.q_start + s + 1] = token + 1;
+    out[L.start_pos + s] = 0;
+    out[L.ctx_len + s] = 1;
+    out[L.slots + s] = cache->max_requests;
+    for (int g = 0; g < G; ++g) {
+      int* dst = out + L.table[g] + (size_t)s * L.width[g];
+      dst[0] = cache->groups[g].pool->capacity();
+      for (int i = 1; i < L.width[g]; ++i) dst[i] = NO_PAGE;
     }
   }
   if (layout) *layout = L;

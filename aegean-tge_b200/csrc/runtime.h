@@ -81,8 +81,10 @@ typedef struct TgeRtStepLayout {
 
 // Reserves what the step needs (admits unknown requests, grows pages; all or nothing) and packs it.
 // tokens[i] / wants[i] point at the i-th portion's token ids and wanted places.  fixed_width > 0 pads
-// every block table to that width and pad_rows > 0 the logit_rows section to that many entries (a
-// captured graph's geometry), else the widest row and the wanted places decide.
+// every block table to that width; pad_rows > 0 pads a step of single tokens to that many portions and
+// the logit_rows section to that many entries (a captured graph's geometry): the idle portions behind
+// the real ones are one token at position 0 of each group's scratch page (id = the pool's capacity)
+// with the scratch state slot (id = max_requests).  Else the widest row and the wanted places decide.
 // Progress is not recorded: call tge_rt_cache_advance after the step ran.
 int tge_rt_step_pack(TgeRtCache* cache, int count, const int64_t* requests, const int* const* tokens,
                      const int* token_counts, const int* const* wants, const int* want_counts, int vocab_size,

@@ -58,13 +58,24 @@ class Staging:
         self.copied[turn] = event
 
 
+def graph_batch(batch: int) -> int:
+    """The batch size whose decode graph serves ``batch`` single tokens: the next of 1, 2, 4, 8, 12, 16, 24,
+    32, 48, 64, 96, 128, ... (powers of two and, from 8 on, the sizes halfway between).  An idle row costs a
+    row of each product and one key, far less than capturing one more graph."""
+    power = 1 << max(batch - 1, 0).bit_length()    # the next power of two at or above
+    middle = power // 2 + power // 4
+    return middle if 8 < batch <= middle else power
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, cache: CacheManager, max_model_len: int, use_graphs: bool = True,
                  max_graph_batch: int = 256, max_graphs: int = 24):
         """``use_graphs``: steps made only of single tokens replay a CUDA graph captured per batch size and
-        context bound.  At most ``max_graphs`` are kept (the one used longest ago goes first); all of them
-        allocate from one memory pool, which is safe because replays never overlap: they run one after the
-        other on the step's stream."""
+        context bound.  Batch sizes are rounded up to a few sizes (:func:`graph_batch`) and the step is padded
+        with idle rows, so that a batch that shrinks request by request does not capture a graph per size.
+        At most ``max_graphs`` are kept (the one used longest ago goes first); all of them allocate from one
+        memory pool, which is safe because replays never overlap: they run one after the other on the step's
+        stream."""
         self.use_graphs = use_graphs and model.graph_safe      # a part that works from host values runs eagerly
         self.max_graph_batch = max_graph_batch
         self.max_graphs = max_graphs
@@ -179,15 +190,16 @@ class ModelRunner:
             while bound < max_ctx:
                 bound *= 2
             bound = min(bound, self.max_model_len)
-            graph = self._graphs.pop((batch, bound), None)
+            padded = min(graph_batch(batch), self.max_graph_batch)
+            graph = self._graphs.pop((padded, bound), None)
             if graph is None:
                 while len(self._graphs) >= self.max_graphs:
                     del self._graphs[next(iter(self._graphs))]
                 if self._graph_pool is None:
                     self._graph_pool = torch.cuda.graph_pool_handle()
-                graph = DecodeGraph(self, batch, bound)
+                graph = DecodeGraph(self, padded, bound)
                 self.graphs_captured += 1
-            self._graphs[(batch, bound)] = graph
+            self._graphs[(padded, bound)] = graph
             logits = graph.run(pack, packed, device_tokens)
             self.ops.launches += graph.kernels
             self.h2d_bytes_last = graph.nbytes
@@ -197,7 +209,7 @@ class ModelRunner:
             elif len(wanted) != batch:
                 logits = logits[torch.tensor(wanted, device=self.device)]
             else:
-                logits = logits.clone()          # the graph's own buffer is overwritten by the next replay
+                logits = logits[:batch].clone()  # the graph's own buffer is overwritten by the next replay
         else:
             need = 4 * tokens + 4 * batch + 1 + groups * batch * self._widest
             if self._staging is None:
@@ -219,7 +231,7 @@ class ModelRunner:
 
 
 class DecodeGraph:
-    """One CUDA graph of a decode step for a fixed number of requests.
+    """One CUDA graph of a decode step for a fixed number of rows: requests, and idle rows behind them.
 
     All index arrays live in one static device buffer that is refilled from a
     pinned host buffer before each replay; launch geometry is captured for a
@@ -290,6 +302,7 @@ class DecodeGraph:
         self.dev.copy_(staging.hosts[turn], non_blocking=True)
         staging.queued(turn)
         if device_tokens is not None:      # the token ids are still on the device: they overwrite the packed placeholders
-            self.dev[self.layout.token_ids:self.layout.token_ids + self.batch].copy_(device_tokens, non_blocking=True)
+            first = self.layout.token_ids
+            self.dev[first:first + device_tokens.numel()].copy_(device_tokens, non_blocking=True)
         self.graph.replay()
         return self.logits

@@ -218,3 +218,51 @@ def test_a_step_that_does_not_fit_takes_nothing():
     assert [(g.pool.free_count, g.tables["a"], g.tables["b"]) for g in m.groups] == before
     pack([Portion("a", [1] * 20, []), Portion("b", [2] * 10, [])])           # the smaller step still runs
     m.check()
+
+
+def test_a_padded_step_gets_idle_portions_on_the_scratch_page():
+    """A step of single tokens packed for more rows than it has: the idle portions stand behind the real ones,
+    one token at position 0, their tables name only the group's scratch page (id = capacity), their state is the
+    scratch slot, and nothing is taken from the pools for them.  A step with a longer portion is not padded."""
+    import ctypes
+
+    import numpy as np
+
+    from aegean_tge_b200 import runtime as rt
+    from aegean_tge_b200.engine.batch import Portion, PortionArrays
+    m = _manager(pages=6, slots=3, specs=(FULL, WINDOW))
+    lib = rt.lib()
+
+    def pack(portions, width, rows):
+        arrays = PortionArrays(m, portions)
+        out = np.full(4096, -7, dtype=np.int32)
+        layout = rt.StepLayout()
+        try:
+            used = rt.check(lib.tge_rt_step_pack(m.native, arrays.count, arrays.handles, arrays.token_ptrs,
+                                                 arrays.token_counts, arrays.want_ptrs, arrays.want_counts, 100, 512,
+                                                 width, rows, out.ctypes.data, out.size, ctypes.byref(layout)))
+        finally:
+            m.forget_dead_handles()
+        return out[:used], layout
+
+    pack([Portion("a", [1] * 20, []), Portion("b", [2] * 3, [])], 0, 0)
+    lib.tge_rt_cache_advance(m.native, (ctypes.c_int64 * 2)(m.handle_of("a"), m.handle_of("b")), (ctypes.c_int * 2)(20, 3), 2)
+    free = [g.pool.free_count for g in m.groups]
+    out, L = pack([Portion("a", [5], [0]), Portion("b", [6], [0])], 4, 5)
+    assert (L.num_seqs, L.num_tokens, L.num_rows, L.max_q_len, L.max_ctx_len) == (5, 5, 2, 1, 21)
+    assert L.total_ints == out.size and not (out == -7).any()             # every entry was written
+    assert out[L.token_ids:L.token_ids + 5].tolist() == [5, 6, 0, 0, 0]
+    assert out[L.positions:L.positions + 5].tolist() == [20, 3, 0, 0, 0]
+    assert out[L.seq_of_token:L.seq_of_token + 5].tolist() == [0, 1, 2, 3, 4]
+    assert out[L.q_start:L.q_start + 6].tolist() == [0, 1, 2, 3, 4, 5]
+    assert out[L.start_pos:L.start_pos + 5].tolist() == [20, 3, 0, 0, 0]
+    assert out[L.ctx_len:L.ctx_len + 5].tolist() == [21, 4, 1, 1, 1]
+    assert out[L.slots:L.slots + 5].tolist() == [m.slot_of("a"), m.slot_of("b"), m.scratch_slot, m.scratch_slot, m.scratch_slot]
+    for g, group in enumerate(m.groups):
+        table = out[L.table[g]:L.table[g] + 5 * 4].reshape(5, 4)
+        assert table[0, :2].tolist() == group.tables["a"][:2] and table[1, 0] == group.tables["b"][0]
+        assert (table[2:] == np.array([group.pool.capacity, -1, -1, -1])).all()
+    assert [g.pool.free_count for g in m.groups] == free                  # a's 21st token fits its second page
+    m.check()
+    with pytest.raises(ValueError, match="only a step of single tokens can be padded"):
+        pack([Portion("a", [5, 6], [0]), Portion("b", [6], [0])], 4, 5)

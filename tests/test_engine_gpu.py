@@ -420,9 +420,9 @@ def test_steps_queued_ahead_change_nothing(model_dirs, tmp_path):
 
 
 def test_decode_graphs_are_capped_and_share_a_pool(model_dirs, oracle):
-    """Decode steps at many batch sizes capture a graph each; only the most recently used ones are kept, they
-    allocate from one pool, and a graph that was dropped is simply captured again: the logits stay those of the
-    plain model whichever graphs live."""
+    """Decode steps at several batch sizes capture a graph for each size class (1, 2, 4, ...); only the most
+    recently used ones are kept, they allocate from one pool, and a graph that was dropped is simply captured
+    again: the logits stay those of the plain model whichever graphs live."""
     name, dtype = "D", "float32"
     engine = _engine(model_dirs, name, dtype, max_requests=6)
     engine.runner.max_graphs = 2
@@ -430,15 +430,48 @@ def test_decode_graphs_are_capped_and_share_a_pool(model_dirs, oracle):
     nexts = [_tokens(name, 6, salt=400 + i) for i in range(5)]
     engine.runner.step([_portion(i, prompts[i], []) for i in range(5)])
     done = [0] * 5
-    for batch in (1, 2, 3, 1, 4, 2):                              # 1 and 2 come back after they were dropped
+    for batch in (1, 2, 3, 1, 4, 2):                              # 3 and 4 share a graph; 1 and 2 come back after they were dropped
         rows = engine.runner.step([_portion(i, [nexts[i][done[i]]]) for i in range(batch)])
         for i in range(batch):
             done[i] += 1
             ref = oracle(name, prompts[i] + nexts[i][:done[i]])[-1]
             assert rel_error(rows[i], ref) < model_tol(dtype, name), (batch, i)
         assert len(engine.runner._graphs) <= 2
-    assert engine.runner.graphs_captured == 6 and engine.runner.graph_replays == 6
+    assert engine.runner.graphs_captured == 5 and engine.runner.graph_replays == 6
     assert engine.runner._graph_pool is not None
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_serve_a_range_of_batch_sizes_with_idle_rows(model_dirs, oracle, dtype):
+    """Above eight rows a decode graph is captured for the next of a few sizes and smaller batches run it with
+    idle rows behind the real ones (one token on the scratch page, state in the scratch slot).  The real rows'
+    logits are the plain model's, the idle rows leave nothing behind in the pages that requests hold, and a
+    batch that shrinks from 12 to 9 keeps replaying one graph."""
+    from aegean_tge_b200.engine.runner import graph_batch
+    assert [graph_batch(b) for b in (1, 2, 3, 4, 5, 8, 9, 12, 13, 16, 17, 25, 33, 49, 64, 65, 200)] == \
+        [1, 2, 4, 4, 8, 8, 12, 12, 16, 16, 24, 32, 48, 64, 64, 96, 256]
+    name = "E"
+    engine = _engine(model_dirs, name, dtype, max_requests=13)
+    count = 12
+    prompts = [_tokens(name, 5 + 3 * i, salt=500 + i) for i in range(count)]
+    nexts = [_tokens(name, 5, salt=600 + i) for i in range(count)]
+    engine.runner.step([_portion(i, prompts[i], []) for i in range(count)])
+    done = [0] * count
+    for batch in (12, 11, 10, 9, 13):
+        if batch == 13:                                           # one more request joins: the next size's graph
+            prompts.append(_tokens(name, 7, salt=700))
+            nexts.append(_tokens(name, 5, salt=701))
+            done.append(0)
+            engine.runner.step([_portion(12, prompts[12], [])])
+        rows = engine.runner.step([_portion(i, [nexts[i][done[i]]]) for i in range(batch)])
+        assert rows.shape[0] == batch
+        for i in range(batch):
+            done[i] += 1
+            ref = oracle(name, prompts[i] + nexts[i][:done[i]])[-1]
+            assert rel_error(rows[i], ref) < model_tol(dtype, name), (batch, i)
+    assert engine.runner.graphs_captured == 2 and engine.runner.graph_replays == 5
+    assert sorted(key[0] for key in engine.runner._graphs) == [12, 16]
+    engine.cache.check()
 
 
 def test_command_line_generates_and_benches(model_dirs, capsys):
