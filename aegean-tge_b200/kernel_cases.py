@@ -99,7 +99,7 @@ def run_sample(args) -> None:
     dev = "cuda:0"
     gen = torch.Generator(device=dev).manual_seed(3)
     scores = torch.randn(args.rows, args.vocab, generator=gen, device=dev) * args.spread
-    temperature = torch.full((args.rows,), 0.8, device=dev)
+    temperature = torch.full((args.rows,), args.temperature, device=dev)
     uniform = torch.rand(args.rows, generator=gen, device=dev)
     top_k = torch.full((args.rows,), args.top_k, dtype=torch.int32, device=dev)
     top_p = torch.full((args.rows,), args.top_p, device=dev)
@@ -116,7 +116,7 @@ def run_sample(args) -> None:
         run()
     stop.record()
     torch.cuda.synchronize()
-    print(f"sample rows={args.rows} vocab={args.vocab} top_k={args.top_k} top_p={args.top_p} min_p={args.min_p}: "
+    print(f"sample rows={args.rows} vocab={args.vocab} temperature={args.temperature} top_k={args.top_k} top_p={args.top_p} min_p={args.min_p}: "
           f"{start.elapsed_time(stop) * 1e3 / args.repeat:.1f} us per call (with the host's launch cost)")
 
 
@@ -148,6 +148,7 @@ def main(argv=None) -> int:
     sample.add_argument("--rows", type=int, default=8)
     sample.add_argument("--vocab", type=int, default=152064)
     sample.add_argument("--spread", type=float, default=3.0)
+    sample.add_argument("--temperature", type=float, default=0.8, help="0: greedy")
     sample.add_argument("--top-k", type=int, default=0)
     sample.add_argument("--top-p", type=float, default=1.0)
     sample.add_argument("--min-p", type=float, default=0.0)

@@ -605,10 +605,15 @@ def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_l
     group = heads // kv_heads
     if max_q_len <= 1 and group <= 16:
         blocks = num_seqs * kv_heads                      # the decode kernel: one block per (request, kv head)
+    elif max_q_len > 1:
+        # Portions of prompts.  Cutting their keys pays only where a block's keys are many and the rows to merge
+        # few: a short portion deep in a long context.  A block takes 64 rows or more; a prompt of 320 tokens cut
+        # in two took 18 us per layer for the attention and 34 us for merging its 8,960 rows of partial states.
+        if max_ctx_len < 2048 or tokens * 4 > max_ctx_len:
+            return 0
+        blocks = -(-tokens // max(64 // group, 1)) * kv_heads
     else:
-        rows = 64 if max_q_len > 1 else (32 if group <= 32 else 64)
-        bq = max(rows // group, 1)
-        blocks = (-(-tokens // bq) if max_q_len > 1 else num_seqs) * kv_heads
+        blocks = num_seqs * kv_heads
     # Two blocks fit on each SM (148 on a B200).  All blocks should run at once: a few more than that and the
     # last ones run alone (batch 16 at context 8,192: 5 splits = 320 blocks took 66 us, 4 splits = 256
     # blocks 52 us; batch 64 at 2,048: 2 splits 56 us, none 47 us).
