@@ -432,7 +432,11 @@ def set_pair_gemm(mode: int) -> None:
     core().tge_gemm_tcgen05_pair_mode(int(mode))
 
 
-FUSED_MAX_TOKENS = 256      # small batches: product + one kernel per token row; larger ones use separate kernels
+# Small batches: the product leaves partial sums and one kernel per token row adds them, normalises or rotates and
+# stores; larger ones use the product's own epilogue and separate kernels.  Prompts of 144 / 160 / 256 tokens at the
+# 7B shape took 4.40 / 4.66 / 5.32 ms the first way and 4.54 / 4.56 / 5.04 ms the second (14B: 8.4 / 9.1 / 11.0 and
+# 8.6 / 9.0 / 10.9), so the change is made between 144 and 160.  (The kernels themselves take up to 256 rows.)
+FUSED_MAX_TOKENS = 144
 
 
 def linear_add_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], stream: torch.Tensor,

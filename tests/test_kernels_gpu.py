@@ -206,7 +206,7 @@ def test_gemm_pair_epilogues(ops, pair_everywhere, M, N, K):
     ops.check_status()
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 3584, 512), (33, 520, 264), (128, 1024, 320), (150, 384, 192)])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 3584, 512), (33, 520, 264), (128, 1024, 320), (140, 384, 192), (150, 384, 192)])
 @pytest.mark.parametrize("defer", [False, True])
 def test_linear_add_norm_and_rows_without_their_factor(ops, M, N, K, defer):
     """stream += x . w^T; the next product's input = RMSNorm(stream) * weight, either complete or (up to 128
@@ -295,7 +295,7 @@ def test_rope_kv_store(ops, dtype, heads, kv_heads, head_dim, rotary):
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,hidden", [(7, 1, 128, 128, 512), (4, 2, 128, 0, 256), (6, 2, 64, 64, 384),
                                                                  (5, 1, 64, 32, 320)])
-@pytest.mark.parametrize("q_lens,starts", [([1, 1, 1], [30, 47, 0]), ([5, 1, 20], [30, 47, 0]), ([70, 58], [3, 16])])
+@pytest.mark.parametrize("q_lens,starts", [([1, 1, 1], [30, 47, 0]), ([5, 1, 20], [30, 47, 0]), ([70, 58], [3, 16]), ([80, 62], [3, 16]), ([90, 70], [3, 6])])
 @pytest.mark.parametrize("deferred", [False, True])
 def test_linear_qkv_rope_store(ops, heads, kv_heads, head_dim, rotary, hidden, q_lens, starts, deferred):
     """The q/k/v product fused with bias, rotation and the cache store, for small batches (one kernel adds the
