@@ -181,10 +181,19 @@ def main() -> int:
     peak, peak_source = peaks.load()
     prefill = bench_prefill(engine, PROMPT, repeat=3, warmup=2, sustain_seconds=0 if args.skip_points else 1.0)
 
+    def rested():
+        """Two seconds without work.  Under its 1 kW cap the GPU runs what comes first after a pause a few per
+        cent faster than what comes later (a decode step of this shape 3.03 ms, 3.2 ms after ten seconds of
+        work), so every figure that is compared with another starts from the same rest."""
+        torch.cuda.synchronize()
+        time.sleep(2.0)
+
     sampler = ClockSampler()
+    rested()
     sampler.start()
     main_run = bench_decode(engine, BATCH, PROMPT, steps=args.steps, warmup=args.warmup)
     clocks = sampler.stop()
+    rested()
     e2e, h2d, d2h = end_to_end(engine, BATCH, args.steps, args.warmup)
     queued_ahead = engine.stats()["steps_queued_ahead"]["used"]
     ops.check_status()
@@ -204,12 +213,15 @@ def main() -> int:
     if not args.skip_points:
         def other_batches():
             for batch in (1, 64):
+                rested()
                 run = bench_decode(engine, batch, PROMPT, steps=short, warmup=args.warmup)
                 points[f"decode_b{batch}"] = rnd(run["tok_s"])
                 points[f"decode_b{batch}_hbm_frac"] = rnd(run["frac"], 4)
+                rested()
                 points[f"e2e_b{batch}"] = rnd(end_to_end(engine, batch, short, args.warmup)[0])
             points["mixed_step_ms"] = rnd(bench_mixed(engine, 63, PROMPT, PROMPT - 63)["ms"], 3)
             cuts = tge.SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1)     # what the cuts cost a step
+            rested()
             points["e2e_b8_top_k50_top_p"] = rnd(end_to_end(engine, BATCH, short, args.warmup, sampling=cuts)[0])
         group("batches", other_batches)
         del engine
@@ -262,7 +274,7 @@ def main() -> int:
             "global_batch": BATCH, "seq_len": PROMPT, "context_limit": CONTEXT, "page_size": PAGE,
             "prefill_tokens": PROMPT, "parallelism": "1 GPU", "cuda_graph": True,
             "l2": "each step reads all weights (>> 126 MB L2), no flush needed",
-            "peaks": peak_source,
+            "peaks": peak_source, "rest": "2 s without work before value, e2e and the batch-1/64 points",
         },
         "clocks": clocks,
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
