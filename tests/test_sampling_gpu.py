@@ -100,6 +100,34 @@ def test_cuts_at_a_real_vocabulary(ops, spread, top_k, top_p, min_p):
         assert between < vocab * 2.0 ** -23, (r, position, expected_position, between)
 
 
+def test_cuts_do_not_depend_on_the_batch(ops):
+    """A row of a large vocabulary is shared by eight blocks when it is sampled alone and by fewer, down to one,
+    in a large batch.  Its token must be the same: the total that top-p refers to is added as integers and the
+    sorted candidates in chunks of a fixed size, so neither depends on who scanned what.  Many draws near every
+    kind of edge (a nucleus that ends between two near-equal candidates, a top-k, a floor) in three batch sizes."""
+    vocab = 152064
+    gen = torch.Generator().manual_seed(77)
+    kinds = [(0, 0.9, 0.0), (40, 0.95, 0.0), (0, 1.0, 0.002), (0, 0.5, 0.0), (3000, 0.8, 0.0), (0, 0.97, 1e-4)]
+    rows = 24
+    logits = (torch.randn(rows, vocab, generator=gen) * torch.linspace(1.5, 5.0, rows)[:, None]).to(DEV)
+    temps = torch.linspace(0.6, 1.4, rows)
+    uniforms = torch.rand(rows, generator=gen)
+    top_k = torch.tensor([kinds[r % len(kinds)][0] for r in range(rows)], dtype=torch.int32)
+    top_p = torch.tensor([kinds[r % len(kinds)][1] for r in range(rows)])
+    min_p = torch.tensor([kinds[r % len(kinds)][2] for r in range(rows)])
+
+    def run(pick):
+        take = lambda t: t[pick].to(DEV).contiguous()
+        return ops.sample_cuts(logits[pick.to(DEV)].contiguous(), take(temps), take(top_k), take(top_p), take(min_p),
+                               take(uniforms)).cpu().tolist()
+
+    alone = [run(torch.tensor([r]))[0] for r in range(rows)]                    # eight blocks per row
+    together = run(torch.arange(rows))                                          # 24 rows: four blocks per row
+    many = run(torch.arange(rows).repeat(5))                                    # 120 rows: one block per row
+    assert together == alone
+    assert many == alone * 5
+
+
 def test_cut_draws_stay_inside_the_cut_and_follow_the_distribution(ops):
     """Many draws with top-k 3 from a known distribution: nothing outside the top three, shares as renormalised."""
     from aegean_tge_b200.sampling import XorShift32
