@@ -572,7 +572,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         lib = attention_lib(head_dim)
         if split_tokens == 0:
             split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, typical_ctx_len or max_ctx_len,
-                                                  heads, kv_heads)
+                                                  heads, kv_heads, bound=max_ctx_len)
         splits = 1 if split_tokens == 0 or max_ctx_len <= split_tokens else -(-max_ctx_len // split_tokens)
         need = lib.tge_attention_mma_scratch_floats(tokens, heads, splits)
         scratch = scratch_floats(need) if need > 0 else None
@@ -598,7 +598,7 @@ MIN_DECODE_PREFIX = 8
 
 
 def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int,
-                           kv_heads: int) -> int:
+                           kv_heads: int, bound: int = 0) -> int:
     """Keys per split for the tensor-core attention: enough blocks to fill the GPU, no more.
 
     The choice depends on the step's shape only through launch geometry; a row's value
@@ -618,15 +618,31 @@ def choose_attention_split(tokens: int, num_seqs: int, max_q_len: int, max_ctx_l
         blocks = -(-tokens // max(64 // group, 1)) * kv_heads
     else:
         blocks = num_seqs * kv_heads
-    # Two blocks fit on each SM (148 on a B200).  All blocks should run at once: a few more than that and the
-    # last ones run alone (batch 16 at context 8,192: 5 splits = 320 blocks took 66 us, 4 splits = 256
-    # blocks 52 us; batch 64 at 2,048: 2 splits 56 us, none 47 us).
-    target = 2 * core().tge_device_sm_count()
-    want_splits = min(target // blocks, -(-max_ctx_len // 128))
-    if want_splits <= 1:
-        return 0
-    split = -(-max_ctx_len // want_splits)
-    return max(128, -(-split // 64) * 64)
+    sms = core().tge_device_sm_count()
+    most = -(-max_ctx_len // 128)                             # no split below 128 keys
+
+    def keys_per_split(splits: int) -> int:
+        return max(128, -(-(-(-max_ctx_len // splits)) // 64) * 64)
+
+    if max_q_len > 1:
+        # Two blocks fit on each SM (148 on a B200) and all blocks should run at once: a few more than that and
+        # the last ones run alone.
+        want_splits = min(2 * sms // blocks, most)
+        return keys_per_split(want_splits) if want_splits > 1 else 0
+    # Single tokens.  About one block per SM is best: every split more is a state more to write and to merge, and
+    # the merging kernel holds sixteen states in registers (A/B in one process, ms per step of the 7B shape, 296
+    # blocks against 148: batch 16 at context 2,048 3.33 / 3.22; batch 8 at 4,096 3.30 / 3.13; batch 4 at 4,096
+    # 3.23 / 3.04; batch 4 at 30,000 4.05 / 3.89; batch 1 at 32,000 3.71 / 3.38).  Two exceptions, both measured:
+    # splits of no more than 256 keys, sixteen at most over the whole bound, are better taken twice as many
+    # (batch 8 at 2,048: 3.03 / 3.07); and requests that alone make half the SMs' worth of blocks or more are
+    # still cut in two once their keys are many (batch 32 at 4,096: 4.29 / 4.57).
+    want_splits = min(sms // blocks, most)
+    twice = min(2 * sms // blocks, most)
+    if twice > want_splits and keys_per_split(twice) <= 256 and -(-max(bound, max_ctx_len) // keys_per_split(twice)) <= 16:
+        want_splits = twice
+    if want_splits <= 1 and 2 * blocks <= 2 * sms and max_ctx_len >= 4096:
+        want_splits = 2
+    return keys_per_split(want_splits) if want_splits > 1 else 0
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
