@@ -1159,6 +1159,7 @@ const CUtensorMap* pool_map(const void* pages, int num_pages, int kv_heads, int 
 
 // Merges the split states of one (token, head): out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s,
 // over the splits that hold keys visible to the row, in split order.
+template <int HELD>                                                  // splits whose state is held in registers
 __global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                        const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                                        int out_stride, int total_tokens, int heads, int window, int split_tokens,
@@ -1169,7 +1170,6 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
   pdl_wait();
   const size_t stride = (size_t)total_tokens * heads;               // slots per split
   const size_t slot0 = (size_t)t * heads + h;
-  constexpr int HELD = 16;                                          // splits whose state is held in registers
   if (num_splits <= HELD) {
     // Every load is asked for before the first result is needed, the row's position among them: one round
     // trip instead of four.  Splits without a key visible to the row are read too (the scratch holds all
@@ -1227,6 +1227,20 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
     }
     out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc * inv);
   }
+}
+
+// Sixteen states in registers serve most steps; a single long request cut into up to 48 splits takes the wider
+// instance, and beyond that the kernel walks the splits in a loop.
+void launch_merge(dim3 grid, cudaStream_t stream, const float* partial_o, const float* partial_ml, const int* positions,
+                  __nv_bfloat16* out, int out_stride, int total_tokens, int heads, int window, int split_tokens,
+                  int num_splits, int first_token) {
+  const int threads = HD >= 128 ? 128 : (HD >= 64 ? 64 : 32);
+  if (num_splits <= 16)
+    tge_launch(attention_merge_kernel<16>, grid, threads, 0, stream, partial_o, partial_ml, positions, out, out_stride,
+               total_tokens, heads, window, split_tokens, num_splits, first_token);
+  else
+    tge_launch(attention_merge_kernel<48>, grid, threads, 0, stream, partial_o, partial_ml, positions, out, out_stride,
+               total_tokens, heads, window, split_tokens, num_splits, first_token);
 }
 
 template <int NWARPS>
@@ -1325,8 +1339,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     if (rc != 0) return rc;
     if (num_splits > 1) {
       dim3 mgrid(tokens - first_token, heads);
-      tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1353,8 +1366,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     if (rc != 0) return rc;
     if (num_splits > 1) {
       dim3 mgrid(tokens - first_token, heads);
-      tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-          (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1390,9 +1402,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
         if (rc2 != 0) return rc2;
         if (num_splits > 1) {
           dim3 mgrid(tokens - first_token, heads);
-          tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-                     (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
-                     window, p.split_tokens, num_splits, first_token);
+          launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
           return tge_launched("attention_merge", 2);
         }
         return 1;
@@ -1414,9 +1424,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
       if (rc != 0) return rc;
       if (num_splits > 1) {
         dim3 mgrid(tokens - first_token, heads);
-        tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-                   (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
-                   window, p.split_tokens, num_splits, first_token);
+        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1439,9 +1447,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
       if (rc != 0) return rc;
       if (num_splits > 1) {
         dim3 mgrid(tokens - first_token, heads);
-        tge_launch(attention_merge_kernel, mgrid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-                   (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads,
-                   window, p.split_tokens, num_splits, first_token);
+        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1461,8 +1467,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   if (rc != 0) return rc;
   if (num_splits > 1) {
     dim3 grid(tokens - first_token, heads);
-    tge_launch(attention_merge_kernel, grid, HD >= 128 ? 128 : (HD >= 64 ? 64 : 32), 0, stream,
-        (const float*)p.partial_o, (const float*)p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+    launch_merge(grid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
     return tge_launched("attention_merge", 2);
   }
   return 1;

@@ -394,6 +394,16 @@ def test_attention_simt(ops, dtype, heads, kv_heads, head_dim):
     assert err < TOL[dtype]
 
 
+@pytest.mark.parametrize("split,window", [(256, 0), (128, 0), (64, 0), (64, 700)])
+def test_attention_merges_many_splits(ops, split, window):
+    """Single tokens deep in a context, their keys cut into 14, 28 and 55 splits: the merging kernel holds up to 16
+    or 48 split states in registers and walks more than that in a loop; with a window most splits hold no
+    visible key.  One far key is made to dominate, so a split dropped or counted twice would show."""
+    err, _, _ = _attention_case(ops, torch.bfloat16, 14, 2, 128, [1, 1, 1], [3499, 1200, 65], window=window, split=split,
+                                spike=(0, 3000 if window else 17))
+    assert err < TOL[torch.bfloat16]
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim", [(7, 1, 128), (28, 4, 64), (6, 2, 48), (40, 2, 16)])
 @pytest.mark.parametrize("page_size,split,window", [(16, 0, 0), (64, 128, 0), (4, 64, 0), (16, 0, 40), (32, 64, 100)])
 def test_attention_routes_leading_single_tokens_to_the_decode_kernel(ops, heads, kv_heads, head_dim, page_size, split,
