@@ -703,32 +703,67 @@ struct RowSums {
   float eps = 0.0f;
 };
 
+// What a k-block (64 of k) of one work item costs, in cycles at about 1.9 GHz, by the width of the token tile.
+// Measured with both operands in L2, one item per SM (or per pair of SMs), as the difference between two lengths of
+// k.  An SM alone needs 2.6 to 3 cycles per token column whatever the width (the tensor core alone 2), so narrow
+// tiles that fill the last wave better cost it nothing; a pair has a floor of about 440 cycles per k-block (its
+// signals cross between two SMs) and is at its best, 2.4 to 2.6 cycles per column, from 176 columns on.  (The
+// 2,048-token products of the 7B shape by width of the pair's tile, 176 / 192 / 208 / 224 / 256 columns: gate and
+// up 342 / 340 / 334 / 352 / 324 us, down 219 / 236 / 180 / 188 / 205 us, q/k/v 55 / 57 / 61 / 66 / 55 us, o 53 / 55 / 47 /
+// 49 / 55 us: the order this table gives.)
+int interpolate(const int (*table)[2], int entries, int bn) {
+  if (bn <= table[0][0]) return table[0][1];
+  for (int i = 1; i < entries; ++i)
+    if (bn <= table[i][0])
+      return table[i - 1][1] + (table[i][1] - table[i - 1][1]) * (bn - table[i - 1][0]) / (table[i][0] - table[i - 1][0]);
+  return table[entries - 1][1];
+}
+int one_sm_kblock_cycles(int bn) {
+  static const int table[][2] = {{32, 290}, {64, 345}, {128, 368}, {160, 428}, {192, 536}, {224, 581}, {256, 757}};
+  return interpolate(table, 7, bn);
+}
+int pair_kblock_cycles(int bn) {
+  static const int table[][2] = {{176, 440}, {192, 482}, {208, 543}, {224, 589}, {240, 640}, {256, 620}};
+  return interpolate(table, 6, bn);
+}
+
+// What a plan costs, in the same cycles: waves of the grid x (k-blocks per item + a fixed cost per item of about
+// six k-blocks) x the cost of a k-block at this tile width.  A cut along k adds a kernel that sums the partial sums
+// (about 3 us) and their way to memory and back (8 bytes per partial sum at about 4 TB/s).
+long long plan_cost(long long items, int places, int k_blocks, int splits, int kblock_cycles, long long outputs) {
+  const long long waves = (items * splits + places - 1) / places;
+  long long cost = waves * ((k_blocks + splits - 1) / splits + 6) * kblock_cycles;
+  if (splits > 1) cost += 5700 + (long long)((double)splits * outputs * 8.0 / 4.0e12 * 1.9e9);
+  return cost;
+}
+
 Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int force_splits) {
   Plan plan;
   const int sms = sm_count();
   const int tiles_w = (N + BM - 1) / BM;
-  int bn;
+  int bn, wide_splits = 0;                 // wide_splits: the cut chosen together with the width (more than 128 tokens)
   if (force_bn > 0) bn = force_bn;
   else if (M <= 16) bn = 16;
   else if (M <= 32) bn = 32;
   else if (M <= 64) bn = 64;
   else if (M <= 128) bn = 128;
   else {
-    // Fewer, fuller waves win.  For every count of token tiles whose width (a multiple of 16) lies in
-    // 128..256 the time is waves x (columns per tile + a fixed cost per tile, in columns); ties go to
-    // the wider tile.  The fixed cost is large: a product of 128 x N x 16 takes the tensor core about as
-    // long at N = 160 as at N = 256 (measured: a tile over K = 5,120 takes 29.4, 30.6 and 31.5 us at 160,
-    // 208 and 256 columns), so a narrower tile pays only when it saves a whole wave.  3584 weight rows x
-    // 2048 tokens: 8 tiles of 256 are 224 items, two waves; 10 tiles of 208 are 280 items, two shorter waves.
-    const int per_tile = 800;
+    // More than 128 tokens: every width of the token tile (a multiple of 16 in 128..256, the tokens shared out
+    // evenly) with every cut along k that the scratch holds, by the cost above; ties go to the wider tile and
+    // the fewer splits.
+    const int k_blocks_here = (K + BK - 1) / BK;
     long long best = -1;
     bn = 256;
     for (int count = (M + 255) / 256;; ++count) {
       const int width = ((M + count - 1) / count + 15) / 16 * 16;
       if (width < 128) break;
       const long long items = (long long)tiles_w * ((M + width - 1) / width);
-      const long long cost = (items + sms - 1) / sms * (width + per_tile);
-      if (best < 0 || cost < best) { best = cost; bn = width; }
+      const int most = force_splits > 0 ? force_splits : (items >= sms || k_blocks_here < 8 ? 1 : (k_blocks_here / 4 < 32 ? k_blocks_here / 4 : 32));
+      for (int s = force_splits > 0 ? force_splits : 1; s <= most; ++s) {
+        if (s > 1 && (long long)s * M * N > scratch_floats) break;
+        const long long cost = plan_cost(items, sms, k_blocks_here, s, one_sm_kblock_cycles(width), (long long)M * N);
+        if (best < 0 || cost < best) { best = cost; bn = width; wide_splits = s; }
+      }
     }
   }
   plan.bn = bn;
@@ -741,6 +776,7 @@ Plan make_plan(int M, int N, int K, long long scratch_floats, int force_bn, int 
   const long long tiles = (long long)tiles_w * ((M + bn - 1) / bn);
   int splits = 1;
   if (force_splits > 0) splits = force_splits;
+  else if (wide_splits > 0) splits = wide_splits;
   else if (tiles < sms && k_blocks >= 8) {
     // Few tiles: cut k so that the work items fill whole waves of the persistent grid.  The cost of a
     // choice is waves x (k-blocks per item + a fixed per-item overhead, in k-blocks); ties go to fewer splits.
@@ -794,18 +830,6 @@ int pair_capacity() {
   return capacity;
 }
 
-// What a plan costs, in k-blocks of a 256-column tile: waves of the grid x (k-blocks per item + a fixed
-// cost per item) x the time of a k-block at this tile width relative to 256 columns (a k-block of 128 x N x 64
-// takes the tensor core about as long at N = 160 as at N = 256, hence the large constant).
-// A cut along k adds a kernel that sums the partial sums (about 3 us) and their way to memory and back (at about
-// 4 TB/s); a k-block of a 256-column tile, 1,056 units, takes about a third of a microsecond.
-long long plan_cost(long long items, int places, int k_blocks, int splits, int bn, long long outputs) {
-  const long long waves = (items * splits + places - 1) / places;
-  long long cost = waves * ((k_blocks + splits - 1) / splits + 6) * (bn + 800);
-  if (splits > 1) cost += 3000 * 3 + (long long)((double)splits * outputs * 8.0 / 4.0e6 * 3000.0);
-  return cost;
-}
-
 // Token tile and cut along k of the pair kernel: the widest tiles first, then enough splits to fill the pairs.
 Plan make_pair_plan(int M, int N, int K, int pairs, long long scratch_floats, long long* cost_out) {
   Plan plan;
@@ -827,7 +851,7 @@ Plan make_pair_plan(int M, int N, int K, int pairs, long long scratch_floats, lo
     const int most = items >= pairs || k_blocks < 8 ? 1 : (k_blocks / 4 < 32 ? k_blocks / 4 : 32);
     for (int splits = 1; splits <= most; ++splits) {
       if (splits > 1 && (long long)splits * M * N > scratch_floats) break;
-      const long long cost = plan_cost(items, pairs, k_blocks, splits, width, (long long)M * N);
+      const long long cost = plan_cost(items, pairs, k_blocks, splits, pair_kblock_cycles(width), (long long)M * N);
       if (best < 0 || cost < best) { best = cost; plan.bn = width; plan.splits = splits; }
     }
     if (first_width) break;
@@ -850,7 +874,12 @@ bool choose_pair(int M, int N, int K, long long scratch_floats, const Plan& sing
   long long pair_cost = 0;
   *pair_plan = make_pair_plan(M, N, K, pairs, scratch_floats, &pair_cost);
   const long long single_items = (long long)((N + BM - 1) / BM) * ((M + single.bn - 1) / single.bn);
-  const long long single_cost = plan_cost(single_items, sm_count(), (K + BK - 1) / BK, single.splits, single.bn, (long long)M * N);
+  long long single_cost = plan_cost(single_items, sm_count(), (K + BK - 1) / BK, single.splits,
+                                    one_sm_kblock_cycles(single.bn), (long long)M * N);
+  // From about a thousand tokens on the pair does better than these figures say (every SM fetches half as many
+  // token rows, which counts once the operands no longer sit in L2: o at 4,096 tokens 78 us against 92, down 375
+  // against 420, where the figures put the SM alone ahead by a few per cent), so it is given 15 % there.
+  if (M >= 1024) single_cost += single_cost * 15 / 100;
   return g_pair_mode == 2 || pair_cost <= single_cost;
 }
 

@@ -225,7 +225,9 @@ def test_a_captured_graph_survives_the_growth_of_the_scratch_buffer():
     if device in ops._scratch:                       # start from the smallest buffer, as a fresh process would
         ops._outgrown.setdefault(device, []).append(ops._scratch.pop(device))
     tokens = _tokens("7B", 40, salt=9)
-    long_prompt = _tokens("7B", 512, salt=10)
+    # 256 tokens: the down product is cut in five along k there (few tiles, a long k), 4.6 M partial sums where the
+    # first buffer holds 4 Mi; longer portions have tiles enough and are not cut
+    long_prompt = _tokens("7B", 256, salt=10)
     outputs = []
     for use_graphs in (True, False):
         engine = _engine("7B", "bfloat16", use_graphs=use_graphs, run_ahead=False, max_tokens=4096)
