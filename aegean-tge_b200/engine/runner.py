@@ -81,6 +81,7 @@ class ModelRunner:
         self.max_graphs = max_graphs
         self._graphs: Dict[tuple, "DecodeGraph"] = {}          # in order of last use
         self._graph_pool = None
+        self._capture_stream = None
         self.graphs_captured = 0
         self.graph_replays = 0
         self.model = model
@@ -275,19 +276,41 @@ class DecodeGraph:
         # all rows' logits are computed; the rows a step wants are picked afterwards
         self.rows = torch.arange(batch, dtype=torch.int32, device=device)
         ops = runner.ops
-        side = torch.cuda.Stream(device=device)
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
-            for _ in range(2):
-                model.forward(self.ctx, self.rows)
-        torch.cuda.current_stream(device).wait_stream(side)
+        # Two eager steps first, on the step's own stream, whose cached blocks they reuse (on a stream of their
+        # own every buffer was a new allocation from the driver: 6 ms became 40 to 150 now and then); then the
+        # capture, on one side stream that all captures share.
+        for _ in range(2):
+            model.forward(self.ctx, self.rows)
         torch.cuda.synchronize(device)
+        if runner._capture_stream is None:
+            runner._capture_stream = torch.cuda.Stream(device=device)
+        side = runner._capture_stream
         before = ops.launches
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=runner._graph_pool):
-            self.logits = model.forward(self.ctx, self.rows)
+        try:
+            self._capture(runner, side)
+        except torch.OutOfMemoryError:
+            # the graphs' pool found no room: give back what the allocator only caches, once, and try again
+            torch.cuda.synchronize(device)
+            torch.cuda.empty_cache()
+            self.graph = torch.cuda.CUDAGraph()
+            self._capture(runner, side)
         self.kernels = ops.launches - before
         ops.launches = before
+
+    def _capture(self, runner: "ModelRunner", side: "torch.cuda.Stream") -> None:
+        """Captures one step on a side stream into the graphs' shared pool.  (``torch.cuda.graph`` would first
+        collect garbage and empty the allocator's cache: with requests in flight that took 30 to 500 ms per
+        capture, most of it freeing and later re-allocating blocks that the steps in between use.)"""
+        device = runner.device
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            self.graph.capture_begin(pool=runner._graph_pool)
+            try:
+                self.logits = runner.model.forward(self.ctx, self.rows)
+            finally:
+                self.graph.capture_end()
+        torch.cuda.current_stream(device).wait_stream(side)
 
     def run(self, pack: Packer, packed: Optional[Callable[[], None]],
             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
