@@ -76,6 +76,65 @@ def check_against_manifest(entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...]
         raise WeightError(missing, unexpected, mismatched)
 
 
+class Uploader:
+    """Moves tensors from the mapped file to the device through a ring of pinned buffers.
+
+    A plain ``tensor.to(device)`` from a mapped file faults its pages in one thread and copies from pageable
+    memory: 2.3 GB/s with the file in the page cache.  Here a few threads copy slices of the file into pinned
+    buffers (the page faults then run side by side), each buffer goes to the device asynchronously and is cast
+    there to the dtype the model wants, and the next buffer is filled meanwhile.
+    """
+
+    CHUNK_BYTES = 64 << 20
+    RING = 3
+    THREADS = 4
+
+    def __init__(self, device: torch.device):
+        from concurrent.futures import ThreadPoolExecutor
+        self.device = device
+        self.cuda = device.type == "cuda"
+        if self.cuda:
+            self.buffers = [torch.empty(self.CHUNK_BYTES, dtype=torch.uint8).pin_memory() for _ in range(self.RING)]
+            self.free_again = [None] * self.RING         # the event after which a buffer may be overwritten
+            self.pool = ThreadPoolExecutor(self.THREADS)
+            self.turn = 0
+
+    def upload(self, host: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        if not self.cuda or host.numel() * host.element_size() < (1 << 20):
+            return host.to(device=self.device, dtype=dtype).contiguous()
+        out = torch.empty(host.shape, dtype=dtype, device=self.device)
+        flat_in, flat_out = host.reshape(-1), out.view(-1)
+        per_chunk = self.CHUNK_BYTES // host.element_size()
+        for first in range(0, flat_in.numel(), per_chunk):
+            count = min(per_chunk, flat_in.numel() - first)
+            turn = self.turn
+            self.turn = (turn + 1) % self.RING
+            if self.free_again[turn] is not None:
+                self.free_again[turn].synchronize()
+            staged = self.buffers[turn].view(host.dtype)[:count]
+            piece = -(-count // self.THREADS)
+            jobs = [self.pool.submit(staged[i:i + piece].copy_, flat_in[first + i:first + i + piece])
+                    for i in range(0, count, piece)]
+            for job in jobs:
+                job.result()
+            if host.dtype == dtype:
+                flat_out[first:first + count].copy_(staged, non_blocking=True)
+            else:                                        # as stored to the device, cast there
+                arrived = torch.empty(count, dtype=host.dtype, device=self.device)
+                arrived.copy_(staged, non_blocking=True)
+                flat_out[first:first + count].copy_(arrived)
+            event = torch.cuda.Event()
+            event.record()
+            self.free_again[turn] = event
+        return out
+
+    def close(self) -> None:
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+            self.pool.shutdown()
+            self.buffers = []
+
+
 def load_checkpoint(model, model_dir: str) -> None:
     """Reads ``model_dir`` and hands the model its tensors on ``model.env.device``."""
     files = ModelFiles(model_dir)
@@ -83,11 +142,14 @@ def load_checkpoint(model, model_dir: str) -> None:
     check_against_manifest({name: (e.dtype, e.shape) for name, e in files.entries.items()}, manifest)
     env = model.env
     tensors: Dict[str, torch.Tensor] = {}
-    for name, (param, _) in manifest.items():
-        if name not in files.entries:
-            continue
-        host = files.read(name)
-        tensors[name] = host.to(device=env.device, dtype=device_dtype(param, env.dtype)).contiguous()
+    uploader = Uploader(env.device)
+    try:
+        for name, (param, _) in manifest.items():
+            if name not in files.entries:
+                continue
+            tensors[name] = uploader.upload(files.read(name), device_dtype(param, env.dtype))
+    finally:
+        uploader.close()
     model.load(tensors)
 
 
