@@ -1483,16 +1483,18 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int decode_prefix, cudaStream_t stream) {
+                              int decode_prefix, int prefix_split_tokens, cudaStream_t stream) {
   TGE_REQUIRE(decode_prefix >= 0 && decode_prefix <= num_seqs, "attention_mma: %d leading single tokens of %d sequences",
               decode_prefix, num_seqs);
+  TGE_REQUIRE(prefix_split_tokens >= 0 && prefix_split_tokens % BKV == 0,
+              "attention_mma: keys per split %d of the leading single tokens must be a multiple of %d", prefix_split_tokens, BKV);
   if (decode_prefix == 0 || max_q_len <= 1 || decode_prefix == num_seqs || kv_heads <= 0 || heads / kv_heads > 16)
     return attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start, start_pos,
                               positions, num_seqs, tokens, max_q_len, max_ctx_len, out, out_stride, heads, kv_heads, scale,
                               window, split_tokens, scratch, status, 0, stream);
   const int first = attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start,
                                        start_pos, positions, decode_prefix, decode_prefix, 1, max_ctx_len, out, out_stride,
-                                       heads, kv_heads, scale, window, split_tokens, scratch, status, 0, stream);
+                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, stream);
   if (first < 0) return first;
   const int rest = attention_dispatch(q, q_stride, k_pages, v_pages, block_table + (size_t)decode_prefix * max_pages, max_pages,
                                       num_pages, page_size, q_start + decode_prefix, start_pos + decode_prefix, positions,

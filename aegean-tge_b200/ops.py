@@ -110,7 +110,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         lib.tge_last_error.restype = ctypes.c_char_p
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
-                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr])
+                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
         if lib.tge_attention_mma_head_dim() != head_dim:
@@ -570,18 +570,25 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                and mma_attention_supports(head_dim, heads, kv_heads, page_size))
     if use_mma:
         lib = attention_lib(head_dim)
+        prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 else 0
+        prefix_split = split_tokens
         if split_tokens == 0:
             split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, typical_ctx_len or max_ctx_len,
                                                   heads, kv_heads, bound=max_ctx_len)
-        splits = 1 if split_tokens == 0 or max_ctx_len <= split_tokens else -(-max_ctx_len // split_tokens)
+            # the single tokens at the head of a mixed step are a decode batch of their own: a few of them deep in
+            # long contexts want their keys cut although the portions beside them do not
+            prefix_split = choose_attention_split(prefix, prefix, 1, max_ctx_len, heads, kv_heads,
+                                                  bound=max_ctx_len) if prefix else 0
+        count = lambda split: 1 if split == 0 or max_ctx_len <= split else -(-max_ctx_len // split)
+        splits = max(count(split_tokens), count(prefix_split) if prefix else 1)
         need = lib.tge_attention_mma_scratch_floats(tokens, heads, splits)
         scratch = scratch_floats(need) if need > 0 else None
         _check(lib.tge_attention_mma(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
                                      block_table.data_ptr(), max_pages, num_pages, page_size, q_start.data_ptr(),
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
-                                     split_tokens, _ptr(scratch), status_word().data_ptr(),
-                                     decode_prefix if decode_prefix >= MIN_DECODE_PREFIX else 0, _stream()), lib)
+                                     split_tokens, _ptr(scratch), status_word().data_ptr(), prefix, prefix_split,
+                                     _stream()), lib)
         return out
     lib = core()
     _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),

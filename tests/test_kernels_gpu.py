@@ -394,6 +394,20 @@ def test_attention_simt(ops, dtype, heads, kv_heads, head_dim):
     assert err < TOL[dtype]
 
 
+def test_leading_single_tokens_deep_in_long_contexts_get_splits_of_their_own(ops):
+    """A mixed step: nine single tokens at contexts of about 4,000 beside a prompt of 300 tokens.  The prompt's
+    keys are not cut; the single tokens, a decode batch of their own, have theirs cut (the choice is automatic
+    here), and one far key dominates a row so that a split lost in the merge would show."""
+    starts = [4000 + 37 * i for i in range(9)] + [0]
+    err, _, _ = _attention_case(ops, torch.bfloat16, 14, 2, 128, [1] * 9 + [300], starts, decode_prefix=9, spike=(0, 123))
+    assert err < TOL[torch.bfloat16]
+    assert ops.choose_attention_split(9, 9, 1, 4400, 14, 2, bound=4400) > 0          # the single tokens' keys are cut
+    starts = [4000 + 37 * i for i in range(9)] + [2900]                                # ... also beside a long portion
+    err, _, _ = _attention_case(ops, torch.bfloat16, 14, 2, 128, [1] * 9 + [1500], starts, decode_prefix=9, spike=(0, 123))
+    assert err < TOL[torch.bfloat16]
+    assert ops.choose_attention_split(1509, 10, 1500, 4400, 14, 2, bound=4400) == 0  # whose keys are not cut
+
+
 @pytest.mark.parametrize("split,window", [(256, 0), (128, 0), (64, 0), (64, 700)])
 def test_attention_merges_many_splits(ops, split, window):
     """Single tokens deep in a context, their keys cut into 14, 28 and 55 splits: the merging kernel holds up to 16
