@@ -591,17 +591,23 @@ __device__ __forceinline__ uint32_t swizzled(int row, int col) {
   return (uint32_t)(block * (BKV * 128) + row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
+// GROUPS: groups of four computing warps.  One group takes every tile; two groups take alternate tiles (the ring then
+// has four stages, each always used by the same group), which doubles what one block pulls out of memory: for
+// launches of no more blocks than SMs, where a block has its SM to itself.
+template <int GROUPS>
+__global__ void __launch_bounds__((4 * GROUPS + 1) * 32) attention_decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  constexpr int WARPS = 4 * GROUPS, STAGES = GROUPS == 1 ? DEC_STAGES : 4, THREADS = (WARPS + 1) * 32;
+  static_assert(STAGES % GROUPS == 0, "a stage must always serve the same group");
   extern __shared__ unsigned char smem_dyn[];
   pdl_trigger();
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;                       // swizzle atoms are 1024 bytes
   unsigned char* generic = smem_dyn + (base - raw);
-  const uint32_t bars = base + DEC_STAGES * TMA_STAGE_BYTES;          // full[stages], then empty[stages]
+  const uint32_t bars = base + STAGES * TMA_STAGE_BYTES;          // full[stages], then empty[stages]
   auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (DEC_STAGES + s); };
-  int* local_table = reinterpret_cast<int*>(generic + DEC_STAGES * TMA_STAGE_BYTES + 64);
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  int* local_table = reinterpret_cast<int*>(generic + STAGES * TMA_STAGE_BYTES + 64);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = uniform_warp_index();
   const int g8 = lane >> 2, t4 = lane & 3;
@@ -620,19 +626,19 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   const int num_tiles = (hi - k_first + BKV - 1) / BKV;
   const int first_page = k_first >> p.page_shift;
   const int last_page = (k_first + num_tiles * BKV - 1) >> p.page_shift;
-  for (int i = first_page + tid; i <= last_page; i += DEC_TMA_THREADS) {
+  for (int i = first_page + tid; i <= last_page; i += THREADS) {
     int page = i < p.max_pages ? p.block_table[(size_t)seq * p.max_pages + i] : -1;
     if (page >= p.num_pages) page = -2;                                // reported below, never fetched
     local_table[i - first_page] = page;
   }
   {
     uint4* fill = reinterpret_cast<uint4*>(generic);
-    for (int i = tid; i < DEC_STAGES * TMA_STAGE_BYTES / 16; i += DEC_TMA_THREADS) fill[i] = make_uint4(0, 0, 0, 0);
+    for (int i = tid; i < STAGES * TMA_STAGE_BYTES / 16; i += THREADS) fill[i] = make_uint4(0, 0, 0, 0);
   }
   if (tid == 0) {
-    for (int s = 0; s < DEC_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), DEC_WARPS);
+      mbar_init(empty_bar(s), 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -645,7 +651,7 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
 
   const int pages_per_tile = BKV >> p.page_shift;
   auto issue = [&](int tile) {                                          // the loading warp's first lane only
-    const int stage = tile % DEC_STAGES;
+    const int stage = tile % STAGES;
     const uint32_t k_dst = base + stage * TMA_STAGE_BYTES, v_dst = k_dst + TMA_TILE_BYTES;
     const uint32_t bar = full_bar(stage);
     int boxes = 0;
@@ -666,7 +672,7 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
       }
     }
   };
-  if (warp == DEC_WARPS) {
+  if (warp == WARPS) {
     // The loading warp runs ahead of the others by up to a ring of tiles; nobody waits for anybody else
     // block-wide.  A stage is refilled once all computing warps have released it.
     if (elect_one()) {
@@ -676,8 +682,8 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
       for (; tile < num_tiles && tile < p.early_tiles && tile < settled; ++tile) issue(tile);
       pdl_wait();
       for (; tile < num_tiles; ++tile) {
-        if (tile >= DEC_STAGES)
-          mbar_wait_bounded(empty_bar(tile % DEC_STAGES), (uint32_t)(tile / DEC_STAGES - 1) & 1u, p.status);
+        if (tile >= STAGES)
+          mbar_wait_bounded(empty_bar(tile % STAGES), (uint32_t)(tile / STAGES - 1) & 1u, p.status);
         issue(tile);
       }
     }
@@ -704,12 +710,13 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   bool bad_page = false;
 
-  for (int it = 0; it < (warp < DEC_WARPS ? num_tiles : 0); ++it) {
-    const int stage = it % DEC_STAGES;
-    const int k0 = k_first + it * BKV + warp * 16;
+  const int group = warp >> 2, w4 = warp & 3;            // this warp's group and its quarter of a tile's keys
+  for (int it = group; it < (warp < WARPS ? num_tiles : 0); it += GROUPS) {
+    const int stage = it % STAGES;
+    const int k0 = k_first + it * BKV + w4 * 16;
     // every warp sees every copy land, also of tiles it has no visible position in: the parity of a wait
     // only tells phases apart while nobody is a whole phase behind
-    mbar_wait_bounded(full_bar(stage), (uint32_t)(it / DEC_STAGES) & 1u, p.status);
+    mbar_wait_bounded(full_bar(stage), (uint32_t)(it / STAGES) & 1u, p.status);
     if (k0 >= hi || k0 + 16 <= lo) {
       if (lane == 0) mbar_arrive(empty_bar(stage));
       continue;
@@ -725,7 +732,7 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
 #pragma unroll
     for (int kc = 0; kc < HD / 16; ++kc) {
       const int mi = lane >> 3;
-      const int n = warp * 16 + (mi >> 1) * 8 + (lane & 7);
+      const int n = w4 * 16 + (mi >> 1) * 8 + (lane & 7);
       uint32_t r0, r1, r2, r3;
       ldmatrix_x4(tK + swizzled(n, kc * 16 + (mi & 1) * 8), r0, r1, r2, r3);
       mma_bf16(s_acc[0], qf[kc], r0, r1);
@@ -780,7 +787,7 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
 #pragma unroll
     for (int dt = 0; dt < HD / 8; dt += 2) {
       const int mi = lane >> 3;
-      const int key = warp * 16 + (mi & 1) * 8 + (lane & 7);
+      const int key = w4 * 16 + (mi & 1) * 8 + (lane & 7);
       uint32_t r0, r1, r2, r3;
       ldmatrix_x4_trans(tV + swizzled(key, (dt + (mi >> 1)) * 8), r0, r1, r2, r3);
       mma_bf16(o_acc[dt], pf, r0, r1);
@@ -793,9 +800,9 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
   if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
 
   float* merge_o = reinterpret_cast<float*>(generic);                   // [warps][16][HD]
-  float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                      // [warps][16][2]
+  float* merge_ml = merge_o + WARPS * 16 * HD;                      // [warps][16][2]
 #pragma unroll
-  for (int i = 0; i < (warp < DEC_WARPS ? 2 : 0); ++i) {
+  for (int i = 0; i < (warp < WARPS ? 2 : 0); ++i) {
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     const int r = g8 + 8 * i;
@@ -809,15 +816,15 @@ __global__ void __launch_bounds__(DEC_TMA_THREADS) attention_decode_tma_kernel(
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < p.group * HD; idx += DEC_TMA_THREADS) {
+  for (int idx = tid; idx < p.group * HD; idx += THREADS) {
     const int r = idx / HD, d = idx - r * HD;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
     const float m_use = m == -INFINITY ? 0.0f : m;
     float l = 0.0f, acc = 0.0f;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       const float scale = exp2f(merge_ml[(w * 16 + r) * 2] - m_use);
       l += scale * merge_ml[(w * 16 + r) * 2 + 1];
       acc += scale * merge_o[((size_t)w * 16 + r) * HD + d];
@@ -1321,20 +1328,34 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     const CUtensorMap* map_v = pool_map(v_pages, num_pages, kv_heads, page_size);
     if (!map_k || !map_v) return -3;
     const int range = (num_splits > 1 ? p.split_tokens : max_ctx_len) + 2 * BKV;
-    const size_t smem = 1024 + (size_t)DEC_STAGES * TMA_STAGE_BYTES + 64 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
+    // No more blocks than SMs, each with many keys: a block has its SM to itself and runs two groups of warps on
+    // alternate tiles (batch 32 at context 2,048, not cut: 3.82 -> 3.66 ms per step).  With few tiles per block the
+    // second group only adds to what has to be set up and merged (batch 4, nine splits of 256 keys: 2.95 -> 3.10).
+    static const bool two_ok = getenv("TGE_DECODE_ONE_GROUP") == nullptr || getenv("TGE_DECODE_ONE_GROUP")[0] == '\0';
+    auto smem_of = [&](int ring) {
+      return 1024 + (size_t)ring * TMA_STAGE_BYTES + 64 + ((size_t)(range >> p.page_shift) + 2) * sizeof(int);
+    };
+    const bool two_groups = two_ok && (long long)num_seqs * kv_heads * num_splits <= tge_sm_count() &&
+                            (num_splits > 1 ? p.split_tokens : max_ctx_len) >= 1536 && smem_of(4) <= 227 * 1024;
+    const int stages = two_groups ? 4 : DEC_STAGES;
+    const size_t smem = smem_of(stages);
     TGE_REQUIRE(smem <= 227 * 1024, "attention_decode: %d keys per block need %zu bytes of shared memory; use smaller splits", range, smem);
-    static size_t configured = 0;
-    if (smem > configured) {
-      cudaError_t err = cudaFuncSetAttribute(attention_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static size_t configured[2] = {0, 0};
+    if (smem > configured[two_groups]) {
+      cudaError_t err = two_groups
+          ? cudaFuncSetAttribute(attention_decode_tma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+          : cudaFuncSetAttribute(attention_decode_tma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (err != cudaSuccess) {
         tge_set_error("attention_decode: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
         return -2;
       }
-      configured = smem;
+      configured[two_groups] = smem;
     }
     p.bq = 1;
+    p.early_tiles = p.early_tiles ? stages : 0;
     dim3 grid(num_seqs, kv_heads, num_splits);
-    tge_launch(attention_decode_tma_kernel, grid, DEC_TMA_THREADS, smem, stream, *map_k, *map_v, p);
+    if (two_groups) tge_launch(attention_decode_tma_kernel<2>, grid, 9 * 32, smem, stream, *map_k, *map_v, p);
+    else tge_launch(attention_decode_tma_kernel<1>, grid, DEC_TMA_THREADS, smem, stream, *map_k, *map_v, p);
     int rc = tge_check_launch("attention_decode_tma");
     if (rc != 0) return rc;
     if (num_splits > 1) {
