@@ -474,6 +474,40 @@ def test_decode_graphs_serve_a_range_of_batch_sizes_with_idle_rows(model_dirs, o
     engine.cache.check()
 
 
+@pytest.mark.parametrize("max_tokens,preempts", [(4096, False), (192, True)])
+def test_many_requests_with_every_sampler_finish_and_give_their_pages_back(model_dirs, max_tokens, preempts):
+    """Forty requests of mixed lengths, greedy, temperature, top-k/top-p and min-p with a repetition penalty, through
+    twelve slots: with room for all, and with so few pages that requests are preempted and start over.  Everyone
+    gets exactly the tokens asked for, every page and slot comes back, no kernel reported a fault."""
+    from aegean_tge_b200 import SamplingParams, ops
+    name = "D"
+    engine = _engine(model_dirs, name, "bfloat16", context=128, max_tokens=max_tokens, max_requests=12, page_size=16,
+                     max_batch_tokens=96)
+    rnd = random.Random(11)
+    vocab = TINY[name][0]["vocab_size"]
+    want = {}
+    for i in range(40):
+        prompt = [rnd.randrange(vocab) for _ in range(rnd.randint(5, 60))]
+        sampling = [None, SamplingParams(temperature=0.9, seed=i + 1),
+                    SamplingParams(temperature=0.8, top_k=10, top_p=0.9, seed=i + 1),
+                    SamplingParams(temperature=1.0, min_p=0.05, repeat_penalty=1.1, seed=i + 1)][i % 4]
+        count = rnd.randint(3, 40)
+        want[engine.add_request(prompt, count, sampling)] = count
+    lengths = want
+    done = {}
+    while engine.has_unfinished():
+        for request in engine.step():
+            done[request.id] = request
+    ops.check_status()
+    engine.cache.check()
+    assert set(done) == set(want)
+    assert all(len(done[i].output) == lengths[i] for i in want)
+    assert all(0 <= t < vocab for r in done.values() for t in r.output)
+    stats = engine.stats()
+    assert (stats["preemptions"] > 0) == preempts
+    assert all(g["free"] == g["capacity"] for g in stats["pages"])
+
+
 def test_command_line_generates_and_benches(model_dirs, capsys):
     """`tge generate` and the three single-step benches on a tiny model: exit codes and the labels of their lines."""
     from aegean_tge_b200.cli import main
